@@ -129,8 +129,7 @@ class PagedGroup:
         self.max_seqs, self.max_pages_per_seq = max_seqs, max_pages_per_seq
         self._api, self._book, self.book_index = host.api(), book, book_index      # book_index: among the paged groups
         shape = (len(layers), num_pages, request.kv_heads, page_size, request.head_dim)
-        self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.k, self.v = self._pools(shape, dtype, device)
         self.device_table = torch.zeros((max_seqs, max_pages_per_seq), dtype=torch.int32, device=device)
         page_bytes = request.kv_heads * page_size * request.head_dim * self.v.element_size()
         self._api.cache_group_storage(book, book_index, self.device_table.data_ptr(), self.device_table.stride(0), self.v.data_ptr(),
@@ -139,6 +138,11 @@ class PagedGroup:
         raw = ctypes.cast(self._api.group_host_table(book, book_index), ctypes.POINTER(ctypes.c_int32))
         self.host_table = torch.from_numpy(np.ctypeslib.as_array(raw, shape=(max_seqs, max_pages_per_seq)))
         self.pages = _Pages(self)
+
+    pools_per_layer = 2                        # keys and values
+
+    def _pools(self, shape, dtype, device):
+        return torch.zeros(shape, dtype=dtype, device=device), torch.zeros(shape, dtype=dtype, device=device)
 
     def table(self, slot: int) -> List[Optional[int]]:
         """The pages of a sequence by logical index; None where a page was given back behind the window."""
@@ -177,7 +181,20 @@ class PagedGroup:
 
     def bytes_per_position(self) -> int:
         r = self.request
-        return 2 * len(self.layers) * r.kv_heads * r.head_dim * self.k.element_size()
+        return self.pools_per_layer * len(self.layers) * r.kv_heads * r.head_dim * self.k.element_size()
+
+
+@register_cache_kind("paged_latent")
+class PagedLatentGroup(PagedGroup):
+    """Pages that hold ONE vector per position and layer (``head_dim`` elements, ``kv_heads`` = 1): a latent from which
+    a mixer derives keys and values itself. A layer's view gives the same pool as ``k`` and as ``v``, so kernels written
+    for pages of keys and values read the latent in both roles. Books, windows, block tables and the zeroing of fresh
+    pages are the paged group's."""
+    pools_per_layer = 1
+
+    def _pools(self, shape, dtype, device):
+        pool = torch.zeros(shape, dtype=dtype, device=device)
+        return pool, pool
 
 
 @register_cache_kind("state")

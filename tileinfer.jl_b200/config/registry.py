@@ -1,6 +1,6 @@
 """The one registry from an architecture's name to its configuration and model.
 
-``config.json`` names its architecture in ``architectures[0]`` (fallback: ``model_type``);
+``config.json`` names its architecture in ``architectures[0]`` or ``architecture`` (fallback: ``model_type``);
 the entry gives the typed configuration class, whose ``model_spec()`` lowers it to the
 per-layer records that :class:`tileinfer_b200.engine.model.DecoderModel` is built from.
 The reference keeps a tuple of supported ``model_type`` strings (src/config.jl:8, 52-53).
@@ -13,6 +13,7 @@ from dataclasses import dataclass
 from typing import Any, Callable, Dict, Mapping, Optional
 
 from .apertus import ApertusConfig, ConfigError
+from .vogilix import VogilixConfig
 
 
 @dataclass(frozen=True)
@@ -40,7 +41,9 @@ def registered_architectures() -> tuple:
 
 
 def resolve_architecture(config: Mapping[str, Any]) -> Architecture:
-    names = config.get("architectures") or []
+    names = list(config.get("architectures") or [])
+    if isinstance(config.get("architecture"), str):          # some designs name themselves with one string
+        names.append(config["architecture"])
     for n in names:
         if n in _ARCHITECTURES:
             return _ARCHITECTURES[n]
@@ -67,3 +70,4 @@ def load_config(model_dir: str):
 
 
 register_architecture(ApertusConfig.architecture, ApertusConfig, model_type=ApertusConfig.model_type)
+register_architecture(VogilixConfig.architecture, VogilixConfig, model_type=VogilixConfig.model_type)

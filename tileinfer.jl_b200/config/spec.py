@@ -56,7 +56,7 @@ class PositionSpec:
 
 @dataclass(frozen=True)
 class NormSpec:
-    kind: str                      # "rmsnorm"
+    kind: str                      # "rmsnorm" | "rmsnorm32" (options: "offset": the checkpoint keeps w - 1)
     size: int
     eps: float
     weight_name: str               # checkpoint tensor name (full)
@@ -90,7 +90,7 @@ class MixerSpec:
 
 @dataclass(frozen=True)
 class FeedForwardSpec:
-    kind: str                      # "xielu_mlp" | user-registered
+    kind: str                      # "xielu_mlp" | "gelu_mlp" | "routed_experts" | user-registered
     prefix: str
     hidden_size: int
     intermediate_size: int = 0
@@ -99,12 +99,35 @@ class FeedForwardSpec:
 
 
 @dataclass(frozen=True)
+class TokenInputSpec:
+    """A per-layer input that depends on the token itself (not on the stream alone): ``kind`` selects the
+    registered part. ``table_name`` is a table shared by all layers with one row per token id, of which this
+    layer reads the columns ``[first_column, first_column + dim)``."""
+    kind: str                      # "gated_embedding" | user-registered
+    prefix: str
+    hidden_size: int
+    dim: int
+    vocab_size: int
+    table_name: str
+    table_columns: int             # columns of the whole table
+    first_column: int
+    eps: float = 1e-6
+    tensor_names: Mapping[str, str] = field(default_factory=dict)
+    options: Mapping[str, Any] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
 class LayerSpec:
-    block: str                     # arrangement: "pre_norm"
+    """``feed_forward`` (with its norm) may be None: a layer that only mixes. ``token_input``: a part that adds
+    something of the token itself to the stream at the end of the layer, for the blocks that know of it.
+    ``options``: constants of the arrangement (a multiplier of the residual branches, for one)."""
+    block: str                     # arrangement: "pre_norm" | "post_norm"
     mixer: MixerSpec
     mixer_norm: NormSpec
-    feed_forward: FeedForwardSpec
-    feed_forward_norm: NormSpec
+    feed_forward: Optional[FeedForwardSpec]
+    feed_forward_norm: Optional[NormSpec]
+    token_input: Optional[TokenInputSpec] = None
+    options: Mapping[str, Any] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)

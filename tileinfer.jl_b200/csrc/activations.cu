@@ -1,0 +1,89 @@
+// Element-wise activations that are not a product's epilogue.
+//
+//   gelu                    y = T(gelu(x)), the exact form 0.5 x (1 + erf(x / sqrt 2)) or the tanh form
+//                           0.5 x (1 + tanh(sqrt(2 / pi) (x + 0.044715 x^3)))
+//   gated_token_embedding   g[t, j] = T(gelu_tanh(g[t, j]) * table[id[t], first + j]): a gate computed from the stream
+//                           times the token's own vector, one slice of a table with a row per token id
+//   gated_unit_limit        y[t, j] = T(a * sigmoid(slope * a) * (b + shift)), a = min(gu[t, j], limit),
+//                           b = clamp(gu[t, ff + j], -limit, limit): a clamped gated unit from its fused gate|up product
+#include "common.cuh"
+
+#define ACT_GELU_ERF 0
+#define ACT_GELU_TANH 1
+
+__device__ __forceinline__ float gelu_erf_value(float z) { return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f)); }
+__device__ __forceinline__ float gelu_tanh_value(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename T>
+__global__ void gelu_kernel(T* out, const T* in, size_t count, int kind) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    pdl_enter();
+    for (; i < count; i += stride) {
+        const float z = to_f32(__ldcg(in + i));
+        out[i] = from_f32<T>(kind == ACT_GELU_TANH ? gelu_tanh_value(z) : gelu_erf_value(z));
+    }
+}
+
+extern "C" int ti_gelu(void* out, const void* in, long long count, int kind, int dtype, cudaStream_t stream) {
+    if (count == 0) return 0;
+    TI_REQUIRE(kind == ACT_GELU_ERF || kind == ACT_GELU_TANH, "gelu: unknown form %d", kind);
+    long long blocks = (count + 255) / 256;
+    if (blocks > ti_sm_count() * 16) blocks = ti_sm_count() * 16;
+    TI_DISPATCH_DTYPE(dtype, (ti_launch(gelu_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (T*)out, (const T*)in, (size_t)count, kind)));
+    return ti_check_launch("gelu");
+}
+
+template <typename T>
+__global__ void gated_token_embedding_kernel(T* g, const T* __restrict__ table, const int* ids, int dim, int columns, int first,
+                                             int vocab, size_t count) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    pdl_enter();
+    for (; i < count; i += stride) {
+        const int t = (int)(i / dim), j = (int)(i % dim);
+        int id = __ldcg(ids + t);
+        if (id < 0 || id >= vocab) id = 0;            // the embedding kernel has reported it
+        const float e = to_f32(table[(size_t)id * columns + first + j]);
+        g[i] = from_f32<T>(gelu_tanh_value(to_f32(__ldcg(g + i))) * e);
+    }
+}
+
+extern "C" int ti_gated_token_embedding(void* g, const void* table, const int* ids, int n, int dim, int columns, int first, int vocab,
+                                        int dtype, cudaStream_t stream) {
+    if (n == 0) return 0;
+    TI_REQUIRE(dim > 0 && first >= 0 && first + dim <= columns, "gated_token_embedding: columns [%d, %d) of %d", first, first + dim, columns);
+    const long long count = (long long)n * dim;
+    long long blocks = (count + 255) / 256;
+    if (blocks > ti_sm_count() * 16) blocks = ti_sm_count() * 16;
+    TI_DISPATCH_DTYPE(dtype, (ti_launch(gated_token_embedding_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (T*)g, (const T*)table,
+                                        ids, dim, columns, first, vocab, (size_t)count)));
+    return ti_check_launch("gated_token_embedding");
+}
+
+template <typename T>
+__global__ void gated_unit_limit_kernel(T* __restrict__ y, const T* gu, int ff, size_t count, float limit, float slope, float shift) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    pdl_enter();
+    for (; i < count; i += stride) {
+        const size_t t = i / ff, j = i % ff;
+        const float a = fminf(to_f32(__ldcg(gu + t * 2 * ff + j)), limit);
+        const float b = fminf(fmaxf(to_f32(__ldcg(gu + t * 2 * ff + ff + j)), -limit), limit);
+        y[i] = from_f32<T>(a / (1.0f + expf(-slope * a)) * (b + shift));
+    }
+}
+
+extern "C" int ti_gated_unit_limit(void* y, const void* gu, int n, int ff, float limit, float slope, float shift, int dtype,
+                                   cudaStream_t stream) {
+    if (n == 0) return 0;
+    TI_REQUIRE(ff > 0, "gated_unit_limit: size %d", ff);
+    const long long count = (long long)n * ff;
+    long long blocks = (count + 255) / 256;
+    if (blocks > ti_sm_count() * 16) blocks = ti_sm_count() * 16;
+    TI_DISPATCH_DTYPE(dtype, (ti_launch(gated_unit_limit_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (T*)y, (const T*)gu, ff,
+                                        (size_t)count, limit, slope, shift)));
+    return ti_check_launch("gated_unit_limit");
+}

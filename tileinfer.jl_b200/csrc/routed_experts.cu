@@ -1,0 +1,210 @@
+// A routed feed-forward: every token goes through `top` of `experts` small gated units, chosen by a router.
+//
+//   router_topk     z = Wr h in 32-bit (one warp per expert and token, lanes stride over the width), score = sigmoid(z);
+//                   the `top` largest (ties to the smaller index) -> ids [n, top], scores [n, top]
+//   expert_plan     the (token, choice) pairs grouped by expert: a row for every pair in expert order, and the list of
+//                   row tiles (expert, first row, rows) that the grouped products walk; one block, counts in shared memory
+//   expert_gather   xs[row] = T(score * h[token]) (the score scales an expert's INPUT) or T(h[token])
+//   grouped_gemm    for every tile: y[row, :] = W[expert] xs[row, :]; as a gated unit W[expert] holds gate rows then up
+//                   rows and y = a * sigmoid(slope * a) * (b + shift), a = min(gate, limit), b = clamp(up, -limit, limit)
+//   expert_combine  out[token] = sum over the token's choices, in choice order, of y[row(token, choice)] (times the score
+//                   where it scales the OUTPUT) + the shared unit's row, in 32-bit, rounded once
+//
+// Nothing here reads a count on the host: grids are sized by upper bounds and blocks beyond the device-side
+// counts leave at once, so a step with a routed feed-forward can be captured in a CUDA graph.
+// Which row a pair gets inside its expert's range depends on the order in which threads arrive; a row's values do
+// not (every row of a product is computed alone, in ascending k), so results are the same bits from run to run.
+#include "tile_gemm.cuh"
+
+#define RT_THREADS 128
+#define RT_MAX_EXPERTS 1024
+
+template <typename T>
+__global__ void router_topk_kernel(const T* h, const T* __restrict__ wr, int width, int experts, int top, int* __restrict__ ids,
+                                   float* __restrict__ scores) {
+    __shared__ float z[RT_MAX_EXPERTS];
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    pdl_enter();
+    const T* row = h + (size_t)t * width;
+    for (int e = warp; e < experts; e += RT_THREADS / 32) {
+        const T* w = wr + (size_t)e * width;
+        float a = 0.f;
+        for (int i = lane; i < width; i += 32) a = fmaf(to_f32(__ldcg(row + i)), to_f32(w[i]), a);
+        a = warp_sum(a);
+        if (lane == 0) z[e] = a;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        for (int j = 0; j < top; ++j) {
+            float best = -INFINITY;
+            int arg = 0x7fffffff;
+            for (int e = lane; e < experts; e += 32)
+                if (z[e] > best) { best = z[e]; arg = e; }           // ascending e: the first of equals stays
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+                if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+            }
+            if (arg >= experts) arg = j;                            // only if every logit left is NaN
+            if (lane == 0) {
+                ids[(size_t)t * top + j] = arg;
+                scores[(size_t)t * top + j] = 1.0f / (1.0f + expf(-best));
+                z[arg] = -INFINITY;
+            }
+            __syncwarp();
+        }
+    }
+}
+
+extern "C" int ti_router_topk(const void* h, const void* wr, int n, int width, int experts, int top, int* ids, float* scores, int dtype,
+                              cudaStream_t stream) {
+    if (n == 0) return 0;
+    TI_REQUIRE(experts >= 1 && experts <= RT_MAX_EXPERTS && top >= 1 && top <= experts, "router_topk: top %d of %d experts", top, experts);
+    TI_DISPATCH_DTYPE(dtype, (ti_launch(router_topk_kernel<T>, dim3(n), dim3(RT_THREADS), 0, stream, (const T*)h, (const T*)wr, width, experts,
+                                        top, ids, scores)));
+    return ti_check_launch("router_topk");
+}
+
+// plan: [0] number of tiles, [1 .. 1 + experts] first row of every expert (and the total), then tiles of 3 words.
+__global__ void expert_plan_kernel(const int* ids, int pairs, int experts, int* __restrict__ pair_row, int* __restrict__ row_pair,
+                                   int* __restrict__ plan) {
+    __shared__ int count[RT_MAX_EXPERTS], first[RT_MAX_EXPERTS + 1];
+    pdl_enter();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&count[__ldcg(ids + p)], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, tiles = 0;
+        int* tile = plan + 2 + experts;
+        for (int e = 0; e < experts; ++e) {
+            first[e] = at;
+            plan[1 + e] = at;
+            for (int r = 0; r < count[e]; r += TG_ROWS) {
+                tile[3 * tiles] = e;
+                tile[3 * tiles + 1] = at + r;
+                tile[3 * tiles + 2] = min(TG_ROWS, count[e] - r);
+                ++tiles;
+            }
+            at += count[e];
+        }
+        first[experts] = at;
+        plan[1 + experts] = at;
+        plan[0] = tiles;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = __ldcg(ids + p);
+        const int row = first[e] + atomicAdd(&count[e], 1);
+        pair_row[p] = row;
+        row_pair[row] = p;
+    }
+}
+
+extern "C" int ti_expert_plan_words(int pairs, int experts) { return 2 + experts + 3 * (pairs < (pairs + TG_ROWS - 1) / TG_ROWS + experts ? pairs : (pairs + TG_ROWS - 1) / TG_ROWS + experts); }
+extern "C" int ti_expert_plan_max_tiles(int pairs, int experts) {
+    const int by_rows = (pairs + TG_ROWS - 1) / TG_ROWS + experts;
+    return pairs < by_rows ? pairs : by_rows;
+}
+
+extern "C" int ti_expert_plan(const int* ids, int pairs, int experts, int* pair_row, int* row_pair, int* plan, cudaStream_t stream) {
+    if (pairs == 0) return 0;
+    TI_REQUIRE(experts >= 1 && experts <= RT_MAX_EXPERTS, "expert_plan: %d experts", experts);
+    ti_launch(expert_plan_kernel, dim3(1), dim3(pairs >= 1024 ? 1024 : 256), 0, stream, ids, pairs, experts, pair_row, row_pair, plan);
+    return ti_check_launch("expert_plan");
+}
+
+template <typename T>
+__global__ void expert_gather_kernel(T* __restrict__ xs, const T* h, const int* row_pair, const float* scores, int top, int width,
+                                     int scale_input) {
+    const int row = blockIdx.x;
+    pdl_enter();
+    const int p = __ldcg(row_pair + row);
+    const float s = scale_input ? __ldcg(scores + p) : 1.0f;
+    const T* src = h + (size_t)(p / top) * width;
+    T* dst = xs + (size_t)row * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_f32<T>(s * to_f32(__ldcg(src + i)));
+}
+
+extern "C" int ti_expert_gather(void* xs, const void* h, const int* row_pair, const float* scores, int pairs, int top, int width,
+                                int scale_input, int dtype, cudaStream_t stream) {
+    if (pairs == 0) return 0;
+    TI_DISPATCH_DTYPE(dtype, (ti_launch(expert_gather_kernel<T>, dim3(pairs), dim3(width >= 1024 ? 256 : 128), 0, stream, (T*)xs, (const T*)h,
+                                        row_pair, scores, top, width, scale_input)));
+    return ti_check_launch("expert_gather");
+}
+
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(TG_THREADS) grouped_gemm_kernel(T* __restrict__ y, const T* x, const T* __restrict__ w, const int* plan,
+                                                                  int experts, int out, int in, float limit, float slope, float shift) {
+    __shared__ TileGemmSmem s;
+    pdl_enter();
+    if ((int)blockIdx.x >= __ldcg(plan)) return;
+    const int* tile = plan + 2 + experts + 3 * blockIdx.x;
+    const int e = __ldcg(tile), row0 = __ldcg(tile + 1), rows = __ldcg(tile + 2);
+    const int col0 = blockIdx.y * TG_COLS, cols = min(TG_COLS, out - col0);
+    const T* xb = x + (size_t)row0 * in;
+    auto xrow = [&](int r) { return xb + (size_t)r * in; };
+    // A gated unit's matrix holds `out` gate rows and then `out` up rows.
+    const T* we = w + (size_t)e * (GATED ? 2 : 1) * out * in + (size_t)col0 * in;
+    float acc[2][4], acc2[2][4];
+    tile_product<T, GATED>(xrow, rows, we, we + (size_t)out * in, (size_t)in, cols, in, acc, acc2, s);
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = 2 * ty + i;
+        if (r >= rows) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c = tx + 16 * j;
+            if (c >= cols) continue;
+            float v = acc[i][j];
+            if (GATED) {
+                const float a = fminf(rnd<T>(v), limit);
+                const float b = fminf(fmaxf(rnd<T>(acc2[i][j]), -limit), limit);
+                v = a / (1.0f + expf(-slope * a)) * (b + shift);
+            }
+            y[(size_t)(row0 + r) * out + col0 + c] = from_f32<T>(v);
+        }
+    }
+}
+
+extern "C" int ti_grouped_gemm(void* y, const void* x, const void* w, const int* plan, int max_tiles, int experts, int out, int in,
+                               int gated, float limit, float slope, float shift, int dtype, cudaStream_t stream) {
+    if (max_tiles == 0) return 0;
+    TI_REQUIRE(out > 0 && in > 0 && experts > 0, "grouped_gemm: bad sizes out=%d in=%d experts=%d", out, in, experts);
+    const dim3 grid(max_tiles, (out + TG_COLS - 1) / TG_COLS);
+    TI_DISPATCH_DTYPE(dtype, {
+        if (gated) ti_launch(grouped_gemm_kernel<T, true>, grid, dim3(TG_THREADS), 0, stream, (T*)y, (const T*)x, (const T*)w, plan, experts, out, in, limit, slope, shift);
+        else ti_launch(grouped_gemm_kernel<T, false>, grid, dim3(TG_THREADS), 0, stream, (T*)y, (const T*)x, (const T*)w, plan, experts, out, in, limit, slope, shift);
+    });
+    return ti_check_launch("grouped_gemm");
+}
+
+template <typename T>
+__global__ void expert_combine_kernel(T* __restrict__ out, const T* y, const int* pair_row, const float* scores, const T* shared,
+                                      int top, int width, int scale_output) {
+    const int t = blockIdx.x;
+    pdl_enter();
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float a = 0.f;
+        for (int j = 0; j < top; ++j) {
+            const int p = t * top + j;
+            const float v = to_f32(__ldcg(y + (size_t)__ldcg(pair_row + p) * width + i));
+            a += scale_output ? __ldcg(scores + p) * v : v;
+        }
+        if (shared != nullptr) a += to_f32(__ldcg(shared + (size_t)t * width + i));
+        out[(size_t)t * width + i] = from_f32<T>(a);
+    }
+}
+
+extern "C" int ti_expert_combine(void* out, const void* y, const int* pair_row, const float* scores, const void* shared, int n, int top,
+                                 int width, int scale_output, int dtype, cudaStream_t stream) {
+    if (n == 0) return 0;
+    TI_DISPATCH_DTYPE(dtype, (ti_launch(expert_combine_kernel<T>, dim3(n), dim3(width >= 1024 ? 256 : 128), 0, stream, (T*)out, (const T*)y,
+                                        pair_row, scores, (const T*)shared, top, width, scale_output)));
+    return ti_check_launch("expert_combine");
+}

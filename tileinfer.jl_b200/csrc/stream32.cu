@@ -1,0 +1,163 @@
+// A residual stream kept in 32-bit, whatever the element type T of the activations and weights is.
+//
+//   embed_positions32   x = E[id] + P[position]                                  (both tables in T, the sum in 32-bit)
+//   cast_rows           h = T(x)
+//   norm32              y = T(x / rms(x) * g(w)),  x in 32-bit or in T
+//   branch_norm_add32   x += mult * d / rms(d) * g(w);  then  h = T(x)  or  h = T(x / rms(x) * g_out(w_out))
+//
+// rms(v) = sqrt(mean(v^2) + eps); g(w) = w, or 1 + w where the checkpoint keeps the gain minus one ("offset"). Everything
+// between the loads and the one rounding on store is 32-bit. d is a sublayer's output: [n, size] in T, or the
+// 32-bit partial sums [s, n, size] of a product that was cut over k (added in split order, not rounded).
+// One block per row; the order of a row's sums depends on the row's size alone.
+#include "common.cuh"
+
+template <typename T>
+__global__ void embed_positions32_kernel(float* __restrict__ x, const T* __restrict__ table, const T* __restrict__ pos_table,
+                                         const int* ids, const int* positions, int hidden, int vocab, int max_positions,
+                                         int* __restrict__ status) {
+    const int t = blockIdx.x;
+    pdl_enter();
+    int id = __ldcg(ids + t), p = __ldcg(positions + t);
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) atomicExch(status, 1 + t);
+        id = 0;
+    }
+    if (p < 0 || p >= max_positions) {
+        if (threadIdx.x == 0) atomicExch(status, 1 + t);
+        p = 0;
+    }
+    const T* e = table + (size_t)id * hidden;
+    const T* q = pos_table + (size_t)p * hidden;
+    float* dst = x + (size_t)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32(e[i]) + to_f32(q[i]);
+}
+
+extern "C" int ti_embed_positions32(float* x, const void* table, const void* pos_table, const int* ids, const int* positions,
+                                    int n_tokens, int hidden, int vocab, int max_positions, int dtype, int* status,
+                                    cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    TI_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0 && max_positions > 0, "embed_positions32: bad sizes n=%d hidden=%d vocab=%d positions=%d",
+               n_tokens, hidden, vocab, max_positions);
+    const int threads = hidden >= 1024 ? 256 : 128;
+    TI_DISPATCH_DTYPE(dtype, (ti_launch(embed_positions32_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream, x, (const T*)table,
+                                        (const T*)pos_table, ids, positions, hidden, vocab, max_positions, status)));
+    return ti_check_launch("embed_positions32");
+}
+
+template <typename T>
+__global__ void cast_rows_kernel(T* __restrict__ h, const float* x, size_t count) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    pdl_enter();
+    for (; i < count; i += stride) h[i] = from_f32<T>(__ldcg(x + i));
+}
+
+extern "C" int ti_cast_rows(void* h, const float* x, long long count, int dtype, cudaStream_t stream) {
+    if (count == 0) return 0;
+    long long blocks = (count + 255) / 256;
+    if (blocks > ti_sm_count() * 16) blocks = ti_sm_count() * 16;
+    TI_DISPATCH_DTYPE(dtype, (ti_launch(cast_rows_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (T*)h, x, (size_t)count)));
+    return ti_check_launch("cast_rows");
+}
+
+// Threads of the row kernels: a function of the row's size alone.
+static int row_threads(int size) { return size >= 4096 ? 512 : size >= 1024 ? 256 : 128; }
+
+template <typename T, typename X>
+__global__ void norm32_kernel(T* __restrict__ y, const X* x, const T* __restrict__ w, int size, float eps, int offset) {
+    __shared__ float scratch[33];
+    const X* row = x + (size_t)blockIdx.x * size;
+    T* dst = y + (size_t)blockIdx.x * size;
+    float ss = 0.f;
+    pdl_enter();
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+        const float v = to_f32(__ldcg(row + i));
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)size + eps);
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+        const float g = offset ? 1.0f + to_f32(w[i]) : to_f32(w[i]);
+        dst[i] = from_f32<T>(to_f32(__ldcg(row + i)) * inv * g);
+    }
+}
+
+extern "C" int ti_norm32(void* y, const void* x, int x_is_f32, const void* w, int n_rows, int size, float eps, int offset,
+                         int dtype, cudaStream_t stream) {
+    if (n_rows == 0) return 0;
+    TI_REQUIRE(size > 0, "norm32: size %d", size);
+    const int threads = row_threads(size);
+    TI_DISPATCH_DTYPE(dtype, {
+        if (x_is_f32) ti_launch(norm32_kernel<T, float>, dim3(n_rows), dim3(threads), 0, stream, (T*)y, (const float*)x, (const T*)w, size, eps, offset);
+        else ti_launch(norm32_kernel<T, T>, dim3(n_rows), dim3(threads), 0, stream, (T*)y, (const T*)x, (const T*)w, size, eps, offset);
+    });
+    return ti_check_launch("norm32");
+}
+
+template <typename T>
+__global__ void branch_norm_add32_kernel(float* x, const T* delta, const float* partials, int n_partials, size_t partial_stride,
+                                         const T* __restrict__ w, int offset, float eps, float mult, T* __restrict__ h,
+                                         const T* __restrict__ w_out, int offset_out, float eps_out, int size) {
+    extern __shared__ float row_d[];           // [size]: the branch's row, then the stream's new row
+    __shared__ float scratch[33];
+    float* row = x + (size_t)blockIdx.x * size;
+    float ss = 0.f;
+    pdl_enter();
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+        float d;
+        if (partials != nullptr) {
+            const float* p = partials + (size_t)blockIdx.x * size + i;
+            d = __ldcg(p);
+            for (int s = 1; s < n_partials; ++s) d += __ldcg(p + (size_t)s * partial_stride);
+        } else {
+            d = to_f32(__ldcg(delta + (size_t)blockIdx.x * size + i));
+        }
+        row_d[i] = d;
+        ss = fmaf(d, d, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)size + eps);
+    float ss2 = 0.f;
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+        const float g = offset ? 1.0f + to_f32(w[i]) : to_f32(w[i]);
+        const float v = __ldcg(row + i) + mult * (row_d[i] * inv * g);
+        row[i] = v;
+        row_d[i] = v;                         // the same thread reads it back below
+        ss2 = fmaf(v, v, ss2);
+    }
+    if (h == nullptr) return;
+    T* dst = h + (size_t)blockIdx.x * size;
+    if (w_out == nullptr) {
+        for (int i = threadIdx.x; i < size; i += blockDim.x) dst[i] = from_f32<T>(row_d[i]);
+        return;
+    }
+    ss2 = block_sum(ss2, scratch);
+    const float inv2 = 1.0f / sqrtf(ss2 / (float)size + eps_out);
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+        const float g = offset_out ? 1.0f + to_f32(w_out[i]) : to_f32(w_out[i]);
+        dst[i] = from_f32<T>(row_d[i] * inv2 * g);
+    }
+}
+
+extern "C" int ti_branch_norm_add32(float* x, const void* delta, const float* partials, int n_partials, long long partial_stride,
+                                    const void* w, int offset, float eps, float mult, void* h, const void* w_out, int offset_out,
+                                    float eps_out, int n_rows, int size, int dtype, cudaStream_t stream) {
+    if (n_rows == 0) return 0;
+    TI_REQUIRE(size > 0 && size <= 50000, "branch_norm_add32: size %d", size);
+    TI_REQUIRE((delta != nullptr) != (partials != nullptr), "branch_norm_add32: give delta or partials, not both");
+    TI_REQUIRE(partials == nullptr || n_partials >= 1, "branch_norm_add32: n_partials %d", n_partials);
+    const int threads = row_threads(size);
+    const size_t smem = (size_t)size * sizeof(float);
+    TI_DISPATCH_DTYPE(dtype, {
+        if (smem > 48 * 1024) {
+            static bool raised = false;       // per element type (this block is instantiated once for each)
+            if (!raised) {
+                cudaFuncSetAttribute(branch_norm_add32_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+                raised = true;
+            }
+        }
+        ti_launch(branch_norm_add32_kernel<T>, dim3(n_rows), dim3(threads), smem, stream, x, (const T*)delta, partials, n_partials,
+                  (size_t)partial_stride, (const T*)w, offset, eps, mult, (T*)h, (const T*)w_out, offset_out, eps_out, size);
+    });
+    return ti_check_launch("branch_norm_add32");
+}

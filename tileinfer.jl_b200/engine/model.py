@@ -25,8 +25,11 @@ def tensor_declarations(spec: ModelSpec) -> List[TensorDecl]:
     for layer in spec.layers:
         decls += lookup("norm", layer.mixer_norm.kind).tensors(layer.mixer_norm)
         decls += lookup("mixer", layer.mixer.kind).tensors(layer.mixer)
-        decls += lookup("norm", layer.feed_forward_norm.kind).tensors(layer.feed_forward_norm)
-        decls += lookup("feed_forward", layer.feed_forward.kind).tensors(layer.feed_forward)
+        if layer.feed_forward is not None:
+            decls += lookup("norm", layer.feed_forward_norm.kind).tensors(layer.feed_forward_norm)
+            decls += lookup("feed_forward", layer.feed_forward.kind).tensors(layer.feed_forward)
+        if layer.token_input is not None:
+            decls += lookup("token_input", layer.token_input.kind).tensors(layer.token_input)
     seen, out = set(), []
     for d in decls:
         if d.name not in seen:
@@ -52,11 +55,18 @@ class DecoderModel:
         for layer in spec.layers:
             position = self._position(layer.mixer.position)
             mixer = lookup("mixer", layer.mixer.kind)(layer.mixer, tensors, rt, position)
-            ffn = lookup("feed_forward", layer.feed_forward.kind)(layer.feed_forward, tensors, rt)
+            ffn = n2 = None
+            if layer.feed_forward is not None:
+                ffn = lookup("feed_forward", layer.feed_forward.kind)(layer.feed_forward, tensors, rt)
+                n2 = lookup("norm", layer.feed_forward_norm.kind)(layer.feed_forward_norm, tensors, rt)
             n1 = lookup("norm", layer.mixer_norm.kind)(layer.mixer_norm, tensors, rt)
-            n2 = lookup("norm", layer.feed_forward_norm.kind)(layer.feed_forward_norm, tensors, rt)
-            self.blocks.append(lookup("block", layer.block)(layer, mixer, ffn, n1, n2))
+            extra = {}
+            if layer.token_input is not None:
+                extra["token_input"] = lookup("token_input", layer.token_input.kind)(layer.token_input, tensors, rt)
+            self.blocks.append(lookup("block", layer.block)(layer, mixer, ffn, n1, n2, **extra))
         self.status = torch.zeros(1, dtype=torch.int32, device=rt.device)
+        # The residual stream has the products' element type unless the architecture keeps it in 32-bit.
+        self.stream_dtype = torch.float32 if spec.options.get("residual_dtype") == "float32" else rt.dtype
 
     def _position(self, pspec):
         key = (pspec.kind, pspec.head_dim, pspec.theta, pspec.scaling, pspec.max_positions, tuple(sorted(pspec.options.items())))
@@ -106,7 +116,7 @@ class DecoderModel:
                     visit(v)
 
         for b in self.blocks:
-            visit([b.mixer, b.feed_forward, b.mixer_norm, b.feed_forward_norm])
+            visit([b.mixer, b.feed_forward, b.mixer_norm, b.feed_forward_norm, getattr(b, "token_input", None)])
         visit([self.final_norm, self.head])
         return total
 
@@ -119,9 +129,13 @@ class DecoderModel:
     def _forward(self, step, cache, logits: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         rt, spec = self.rt, self.spec
         n = step.n_tokens
-        x = rt.buffer("model.x", (n, spec.hidden_size))
+        x = rt.buffer("model.x", (n, spec.hidden_size), self.stream_dtype)
         h = rt.buffer("model.h", (n, spec.hidden_size))
-        self.embedding.forward(step.token_ids, x, self.status)
+        embed_step = getattr(self.embedding, "forward_step", None)
+        if embed_step is not None:
+            embed_step(step, x, self.status)
+        else:
+            self.embedding.forward(step.token_ids, x, self.status)
         order = spec.order
         self.blocks[order[0]].input_norm.forward(x, h) if order else self.final_norm.forward(x, h)
         for occ, li in enumerate(order):

@@ -113,6 +113,10 @@ def lib():
     wrapped.ti_sampling_uniform = handle.ti_sampling_uniform
     wrapped.ti_argmax_chunks = handle.ti_argmax_chunks
     wrapped.ti_gemm_tcgen05_decode_plan = handle.ti_gemm_tcgen05_decode_plan
+    for name in ("ti_expert_plan_words", "ti_expert_plan_max_tiles"):
+        fn = getattr(handle, name)
+        fn.restype, fn.argtypes = c_int, [c_int, c_int]
+        setattr(wrapped, name, fn)
     wrapped.handle = handle
     for name, args in _SIGNATURES.items():
         fn = getattr(handle, name)
@@ -154,3 +158,21 @@ _SIGNATURES_FAST = {
     "ti_attention_prefill_tc": [_P, _P, _P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _F, _I, _I, _I, _I, _I, _P, _P],
 }
 _SIGNATURES.update(_SIGNATURES_FAST)
+
+# The 32-bit residual stream, latent attention's inputs, per-head and per-expert products, activations.
+_SIGNATURES.update({
+    "ti_embed_positions32": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+    "ti_cast_rows": [_P, _P, _L, _I, _P],
+    "ti_norm32": [_P, _P, _I, _P, _I, _I, _F, _I, _I, _P],
+    "ti_branch_norm_add32": [_P, _P, _P, _I, _L, _P, _I, _F, _F, _P, _P, _I, _F, _I, _I, _I, _P],
+    "ti_latent_inputs": [_P, _L, _P, _I, _L, _P, _P, _P, _P, _F, _P, _I, _I, _I, _I, _P],
+    "ti_head_gemm": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _I, _P],
+    "ti_gelu": [_P, _P, _L, _I, _I, _P],
+    "ti_gated_token_embedding": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "ti_gated_unit_limit": [_P, _P, _I, _I, _F, _F, _F, _I, _P],
+    "ti_router_topk": [_P, _P, _I, _I, _I, _I, _P, _P, _I, _P],
+    "ti_expert_plan": [_P, _I, _I, _P, _P, _P, _P],
+    "ti_expert_gather": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "ti_grouped_gemm": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _F, _I, _P],
+    "ti_expert_combine": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+})

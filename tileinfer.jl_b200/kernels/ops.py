@@ -189,3 +189,154 @@ def sample(logits, out, temperature, top_k, top_p, seeds, counters, also=None, c
     check(lib().ti_sample_shared(logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1], temperature, top_k,
                                  top_p, seeds.data_ptr(), counters.data_ptr(), out.data_ptr(), _ptr(also), cluster_blocks,
                                  _stream()), "sample")
+
+
+# ---------------------------------------------------------------- a residual stream in 32-bit
+ACT_GELU_ERF, ACT_GELU_TANH = 0, 1
+
+
+def embed_positions32(x, table, pos_table, ids, positions, status):
+    """x[t] = table[ids[t]] + pos_table[positions[t]], summed and kept in 32-bit."""
+    _need(x, "x", torch.float32); _need(table, "table"); _need(pos_table, "pos_table", table.dtype)
+    _need(ids, "ids", torch.int32); _need(positions, "positions", torch.int32); _need(status, "status", torch.int32)
+    n, hidden = x.shape
+    if table.shape[1] != hidden or pos_table.shape[1] != hidden:
+        raise KernelError(f"embed_positions32: tables {tuple(table.shape)}, {tuple(pos_table.shape)} for a width of {hidden}")
+    check(lib().ti_embed_positions32(x.data_ptr(), table.data_ptr(), pos_table.data_ptr(), ids.data_ptr(), positions.data_ptr(), n,
+                                     hidden, table.shape[0], pos_table.shape[0], dtype_code(table.dtype), status.data_ptr(), _stream()),
+          "embed_positions32")
+
+
+def cast_rows(h, x):
+    """h = x rounded to h's element type; x is 32-bit."""
+    _need(h, "h"); _need(x, "x", torch.float32)
+    check(lib().ti_cast_rows(h.data_ptr(), x.data_ptr(), x.numel(), dtype_code(h.dtype), _stream()), "cast_rows")
+
+
+def norm32(y, x, w, eps, offset=False):
+    """y = x / rms(x) * (1 + w if offset else w), computed in 32-bit; x is 32-bit or of y's type."""
+    _need(y, "y"); _need(x, "x"); _need(w, "w", y.dtype)
+    if x.dtype not in (torch.float32, y.dtype):
+        raise KernelError(f"norm32: input must be float32 or {y.dtype}")
+    size = x.shape[-1]
+    check(lib().ti_norm32(y.data_ptr(), x.data_ptr(), int(x.dtype == torch.float32), w.data_ptr(), x.numel() // size, size, eps,
+                          int(bool(offset)), dtype_code(y.dtype), _stream()), "norm32")
+
+
+def branch_norm_add32(x, delta, w, eps, mult, offset=False, h=None, out_norm=None):
+    """x += mult * delta / rms(delta) * g(w) in 32-bit (``delta``: [n, size] of w's type, or 32-bit partial sums
+    [s, n, size]); then, with ``h``, h = x rounded, or h = x / rms(x) * g(w_out) for ``out_norm`` = (w_out, eps, offset)."""
+    _need(x, "x", torch.float32); _need(w, "w")
+    n, size = x.shape
+    if delta.dim() == 3:
+        _need(delta, "partial sums", torch.float32)
+        d_args = (None, delta.data_ptr(), delta.shape[0], delta.stride(0))
+    else:
+        _need(delta, "delta", w.dtype)
+        d_args = (delta.data_ptr(), None, 0, 0)
+    if h is not None:
+        _need(h, "h", w.dtype)
+    w_out, eps_out, offset_out = out_norm if out_norm is not None else (None, 0.0, False)
+    if w_out is not None:
+        _need(w_out, "w_out", w.dtype)
+    check(lib().ti_branch_norm_add32(x.data_ptr(), *d_args, w.data_ptr(), int(bool(offset)), eps, mult, _ptr(h), _ptr(w_out),
+                                     int(bool(offset_out)), eps_out, n, size, dtype_code(w.dtype), _stream()), "branch_norm_add32")
+
+
+def latent_inputs(rows, cq, pool, wq, wkv, eps, slots, q_rank, kv_rank):
+    """rows [n, q_rank + kv_rank] (or 32-bit partial sums [s, n, ...]) -> cq [n, q_rank] and the key/value latent of every
+    token at its place ``slots[t]`` of ``pool`` [positions, kv_rank]; both RMS-normed in 32-bit with plain weights."""
+    _need(cq, "cq"); _need(pool, "pool", cq.dtype); _need(wq, "wq", cq.dtype); _need(wkv, "wkv", cq.dtype); _need(slots, "slots", torch.int32)
+    if rows.dim() == 3:
+        _need(rows, "partial sums", torch.float32)
+        args = (None, 0, rows.data_ptr(), rows.shape[0], rows.stride(0))
+        n = rows.shape[1]
+    else:
+        _need(rows, "rows", cq.dtype, contiguous=False)
+        if rows.stride(1) != 1:
+            raise KernelError("latent_inputs: rows must be dense")
+        args = (rows.data_ptr(), rows.stride(0), None, 0, 0)
+        n = rows.shape[0]
+    check(lib().ti_latent_inputs(*args, cq.data_ptr(), pool.data_ptr(), wq.data_ptr(), wkv.data_ptr(), eps, slots.data_ptr(), n,
+                                 q_rank, kv_rank, dtype_code(cq.dtype), _stream()), "latent_inputs")
+
+
+def head_gemm(y, x, w):
+    """y[t, h, :] = w[h] x[t, h, :] for w [heads, out_h, in_h], x [n, heads, in_h], y [n, heads, out_h]."""
+    _need(y, "y"); _need(x, "x", y.dtype); _need(w, "w", y.dtype)
+    heads, out_h, in_h = w.shape
+    n = x.shape[0]
+    if tuple(x.shape) != (n, heads, in_h) or tuple(y.shape) != (n, heads, out_h):
+        raise KernelError(f"head_gemm: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)} do not fit")
+    check(lib().ti_head_gemm(y.data_ptr(), heads * out_h, x.data_ptr(), heads * in_h, w.data_ptr(), n, heads, out_h, in_h,
+                             dtype_code(y.dtype), _stream()), "head_gemm")
+
+
+def gelu(out, x, kind=ACT_GELU_ERF):
+    _need(out, "out"); _need(x, "x", out.dtype)
+    check(lib().ti_gelu(out.data_ptr(), x.data_ptr(), x.numel(), kind, dtype_code(out.dtype), _stream()), "gelu")
+
+
+def gated_token_embedding(g, table, ids, first):
+    """g[t, j] = gelu_tanh(g[t, j]) * table[ids[t], first + j], in place."""
+    _need(g, "g"); _need(table, "table", g.dtype); _need(ids, "ids", torch.int32)
+    n, dim = g.shape
+    check(lib().ti_gated_token_embedding(g.data_ptr(), table.data_ptr(), ids.data_ptr(), n, dim, table.shape[1], first, table.shape[0],
+                                         dtype_code(g.dtype), _stream()), "gated_token_embedding")
+
+
+def gated_unit_limit(y, gu, limit, slope, shift):
+    """y[t, j] = a * sigmoid(slope * a) * (b + shift), a = min(gu[t, j], limit), b = clamp(gu[t, ff + j], -limit, limit)."""
+    _need(y, "y"); _need(gu, "gu", y.dtype)
+    n, ff = y.shape
+    if tuple(gu.shape) != (n, 2 * ff):
+        raise KernelError(f"gated_unit_limit: gu {tuple(gu.shape)} for y {tuple(y.shape)}")
+    check(lib().ti_gated_unit_limit(y.data_ptr(), gu.data_ptr(), n, ff, limit, slope, shift, dtype_code(y.dtype), _stream()),
+          "gated_unit_limit")
+
+
+def router_topk(h, wr, top, ids, scores):
+    """ids, scores [n, top]: the ``top`` experts of every row with the largest sigmoid(wr h), logits in 32-bit."""
+    _need(h, "h"); _need(wr, "wr", h.dtype); _need(ids, "ids", torch.int32); _need(scores, "scores", torch.float32)
+    n, width = h.shape
+    check(lib().ti_router_topk(h.data_ptr(), wr.data_ptr(), n, width, wr.shape[0], top, ids.data_ptr(), scores.data_ptr(),
+                               dtype_code(h.dtype), _stream()), "router_topk")
+
+
+def expert_plan_sizes(pairs: int, experts: int):
+    """(words of the plan, most row tiles) for ``pairs`` (token, choice) pairs over ``experts`` experts."""
+    return int(lib().ti_expert_plan_words(pairs, experts)), int(lib().ti_expert_plan_max_tiles(pairs, experts))
+
+
+def expert_plan(ids, experts, pair_row, row_pair, plan):
+    _need(ids, "ids", torch.int32); _need(pair_row, "pair_row", torch.int32); _need(row_pair, "row_pair", torch.int32)
+    _need(plan, "plan", torch.int32)
+    check(lib().ti_expert_plan(ids.data_ptr(), ids.numel(), experts, pair_row.data_ptr(), row_pair.data_ptr(), plan.data_ptr(), _stream()),
+          "expert_plan")
+
+
+def expert_gather(xs, h, row_pair, scores, top, scale_input=True):
+    _need(xs, "xs"); _need(h, "h", xs.dtype); _need(row_pair, "row_pair", torch.int32); _need(scores, "scores", torch.float32)
+    check(lib().ti_expert_gather(xs.data_ptr(), h.data_ptr(), row_pair.data_ptr(), scores.data_ptr(), xs.shape[0], top, xs.shape[1],
+                                 int(bool(scale_input)), dtype_code(xs.dtype), _stream()), "expert_gather")
+
+
+def grouped_gemm(y, x, w, plan, max_tiles, gated=False, limit=0.0, slope=0.0, shift=0.0):
+    """Rows of x grouped by expert (``plan``): y[row] = w[expert] x[row]; ``gated``: w [experts, 2 * out, in] holds gate
+    rows then up rows and y is the clamped gated unit's activation."""
+    _need(y, "y"); _need(x, "x", y.dtype); _need(w, "w", y.dtype); _need(plan, "plan", torch.int32)
+    experts, rows_w, k = w.shape
+    out = rows_w // 2 if gated else rows_w
+    if x.shape[1] != k or y.shape[1] != out or x.shape[0] != y.shape[0]:
+        raise KernelError(f"grouped_gemm: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)} do not fit")
+    check(lib().ti_grouped_gemm(y.data_ptr(), x.data_ptr(), w.data_ptr(), plan.data_ptr(), max_tiles, experts, out, k, int(bool(gated)),
+                                limit, slope, shift, dtype_code(y.dtype), _stream()), "grouped_gemm")
+
+
+def expert_combine(out, y, pair_row, scores, shared, top, scale_output=False):
+    _need(out, "out"); _need(y, "y", out.dtype); _need(pair_row, "pair_row", torch.int32); _need(scores, "scores", torch.float32)
+    if shared is not None:
+        _need(shared, "shared", out.dtype)
+    n, width = out.shape
+    check(lib().ti_expert_combine(out.data_ptr(), y.data_ptr(), pair_row.data_ptr(), scores.data_ptr(), _ptr(shared), n, top, width,
+                                  int(bool(scale_output)), dtype_code(out.dtype), _stream()), "expert_combine")

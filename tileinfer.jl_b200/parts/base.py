@@ -21,6 +21,8 @@ Interfaces (duck-typed; the base classes document them):
 * ``FeedForward(spec, tensors, rt)``: ``forward(h, step) -> delta``, token by token.
 * ``Block(layer_spec, mixer, feed_forward, mixer_norm, feed_forward_norm)``:
   ``forward(x, h, step, cache, next_norm, h_out)``.
+* ``TokenInput(spec, tensors, rt)`` (``parts/token_input.py``): ``forward(h, step) -> y`` and a ``norm`` through which a
+  block that knows of it adds y to the stream at the end of the layer.
 * ``Embedding(model_spec, tensors, rt)`` and ``Head(model_spec, tensors, rt, embedding)``: the two ends of the
   model (``ModelSpec.embedding_kind`` / ``head_kind``), so that an embedding multiplier or a scaled or capped
   logit is a registered part, not an edit of the decoder.
@@ -119,10 +121,14 @@ class FeedForward(Part):
 class Embedding(Part):
     """Token ids to the residual stream. ``__init__(spec: ModelSpec, tensors, rt)``; ``table`` is the matrix a tied
     head shares; ``forward(token_ids, out, status)`` writes ``out`` [n, hidden] (``status``: a device word that
-    receives 1 + the index of a token whose id is outside the vocabulary)."""
+    receives 1 + the index of a token whose id is outside the vocabulary). An embedding that needs more of the step
+    than the ids (positions, for one) overrides ``forward_step(step, out, status)``."""
 
     def forward(self, token_ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
+
+    def forward_step(self, step, out: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
+        return self.forward(step.token_ids, out, status)
 
 
 class Head(Part):
@@ -134,7 +140,7 @@ class Head(Part):
 
 
 _REGISTRIES: Dict[str, Dict[str, Any]] = {"mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {},
-                                          "embedding": {}, "head": {}}
+                                          "embedding": {}, "head": {}, "token_input": {}}
 
 
 def _register(family: str, kind: str, cls):

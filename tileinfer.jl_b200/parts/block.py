@@ -1,4 +1,5 @@
 """Arrangement of a layer's parts. ``pre_norm``: x += mixer(norm1(x)); x += ffn(norm2(x)).
+``post_norm``: x += m norm1(mixer(x)); x += m norm2(ffn(x)); x += m token_input(x), on a 32-bit stream.
 
 Each residual add is fused with the norm that follows it, so a block receives the already
 normed input ``h`` and produces the next block's normed input with ``next_norm`` (the next
@@ -8,6 +9,7 @@ block's mixer norm, or the model's final norm), as AntoineBut/TileInfer.jl's ste
 from __future__ import annotations
 
 from .base import register_block
+from .norm import StreamCast
 
 
 @register_block("pre_norm")
@@ -27,4 +29,36 @@ class PreNormBlock:
         self.feed_forward_norm.add_forward(x, delta, h)
         delta = self.feed_forward.forward(h, step)
         next_norm.add_forward(x, delta, h_out)
+        return h_out
+
+
+@register_block("post_norm")
+class PostNormBlock:
+    """The norm sits on each sublayer's output, the sublayers read the stream itself, and every branch is added with
+    the multiplier ``residual_mult`` of the layer's options: x += m * norm1(mixer(x)); x += m * norm2(ffn(x)) (a layer
+    may have no feed-forward); then, if the layer has a token input, x += m * its normalised output. The stream x is
+    32-bit; ``h`` is its rounding to the products' element type, rewritten by the kernel that updates x. The norms
+    are of a kind that offers ``branch_add`` (``rmsnorm32``)."""
+
+    def __init__(self, spec, mixer, feed_forward, mixer_norm, feed_forward_norm, token_input=None):
+        self.spec = spec
+        self.mixer, self.feed_forward, self.token_input = mixer, feed_forward, token_input
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+        self.mult = float(spec.options.get("residual_mult", 1.0))
+        self._cast = StreamCast()
+
+    @property
+    def input_norm(self):
+        return self._cast
+
+    def forward(self, x, h, step, cache, next_norm, h_out):
+        branches = [(self.mixer_norm, lambda: self.mixer.forward(h, step, cache))]
+        if self.feed_forward is not None:
+            branches.append((self.feed_forward_norm, lambda: self.feed_forward.forward(h, step)))
+        if self.token_input is not None:
+            branches.append((self.token_input.norm, lambda: self.token_input.forward(h, step)))
+        for i, (norm, run) in enumerate(branches):
+            delta = run()
+            last = i + 1 == len(branches)
+            norm.branch_add(x, delta, self.mult, h_out if last else h, next_norm if last else self._cast)
         return h_out

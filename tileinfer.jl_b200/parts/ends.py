@@ -41,3 +41,24 @@ class LinearHead(Head):
 
     def forward(self, h, logits):
         return self.linear.forward(h, logits, ops.EPI_F32_OUT)
+
+
+@register_embedding("lookup_learned_positions")
+class PositionedEmbedding(Embedding):
+    """x = E[token] + P[position]: a learned vector per position (unscaled) added to the token's row, the sum kept in
+    32-bit. ``ModelSpec.options["position_table"]`` names P [max_positions, hidden]. The stream it writes is 32-bit
+    (``options["residual_dtype"] == "float32"``)."""
+
+    def __init__(self, spec: ModelSpec, tensors, rt):
+        self.table = rt.param(tensors[spec.embed_name])
+        self.positions = rt.param(tensors[spec.options["position_table"]])
+
+    @classmethod
+    def tensors(cls, spec: ModelSpec):
+        o = spec.options
+        return [TensorDecl(spec.embed_name, (spec.vocab_size, spec.hidden_size), ("normal", o.get("embed_init_std", spec.init_std))),
+                TensorDecl(o["position_table"], (spec.max_positions, spec.hidden_size), ("normal", o.get("position_init_std", spec.init_std)))]
+
+    def forward_step(self, step, out, status):
+        ops.embed_positions32(out, self.table, self.positions, step.token_ids, step.positions, status)
+        return out

@@ -57,3 +57,33 @@ class XieluMLP(FeedForward):
         self.up.forward(h, act, ops.EPI_XIELU, self.act)
         out = self.rt.buffer("feed_forward.delta", (n, self.spec.hidden_size))
         return self.down.forward(act, out, allow_partials=True)
+
+
+@register_feed_forward("gelu_mlp")
+class GeluMLP(FeedForward):
+    """down(act(up h)), no gate and no biases; ``options["activation"]``: "gelu_erf" (the exact form) or "gelu_tanh"."""
+
+    def __init__(self, spec: FeedForwardSpec, tensors, rt):
+        self.spec, self.rt = spec, rt
+        n, p = spec.tensor_names, spec.prefix
+        self.up = Linear(rt.param(tensors[p + n["up"]]), rt, "up")
+        self.down = Linear(rt.param(tensors[p + n["down"]]), rt, "down")
+        kinds = {"gelu_erf": ops.ACT_GELU_ERF, "gelu_tanh": ops.ACT_GELU_TANH}
+        act = spec.options.get("activation", "gelu_erf")
+        if act not in kinds:
+            raise ValueError(f"gelu_mlp: activation {act!r} (known: {', '.join(kinds)})")
+        self.kind = kinds[act]
+
+    @classmethod
+    def tensors(cls, spec: FeedForwardSpec):
+        n, p, o = spec.tensor_names, spec.prefix, spec.options
+        return [TensorDecl(p + n["up"], (spec.intermediate_size, spec.hidden_size), ("normal", o.get("init_std_up", 0.02))),
+                TensorDecl(p + n["down"], (spec.hidden_size, spec.intermediate_size), ("normal", o.get("init_std_down", 0.02)))]
+
+    def forward(self, h, step):
+        n = h.shape[0]
+        act = self.rt.buffer("feed_forward.act", (n, self.spec.intermediate_size))
+        self.up.forward(h, act)
+        ops.gelu(act, act, self.kind)
+        out = self.rt.buffer("feed_forward.delta", (n, self.spec.hidden_size))
+        return self.down.forward(act, out, allow_partials=True)

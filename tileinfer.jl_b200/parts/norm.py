@@ -31,3 +31,49 @@ class RMSNorm(Norm):
         else:
             ops.add_rmsnorm(x, delta, self.weight, out, self.eps)
         return out
+
+
+@register_norm("rmsnorm32")
+class RMSNorm32(Norm):
+    """RMS norm computed in 32-bit with one rounding at the end: y = x / sqrt(mean(x^2) + eps) * g(w), g(w) = w, or
+    1 + w with the option ``offset`` (the checkpoint keeps the gain minus one). The input may be a 32-bit residual stream.
+
+    Besides ``forward`` it serves blocks that normalise a sublayer's OUTPUT: ``branch_add(x, delta, mult, h, next_norm)``
+    does x += mult * norm(delta) on a 32-bit stream and, in the same kernel, prepares the next reader's input
+    (``next_norm``: another norm of this kind or a :class:`StreamCast`)."""
+
+    def __init__(self, spec: NormSpec, tensors, rt):
+        self.spec, self.rt = spec, rt
+        self.weight = rt.param(tensors[spec.weight_name])
+        self.eps = float(spec.eps)
+        self.offset = bool(spec.options.get("offset", False))
+
+    @classmethod
+    def tensors(cls, spec: NormSpec):
+        std = spec.options.get("init_std", 0.02)
+        init = ("normal", std) if spec.options.get("offset", False) else ("one_plus_normal", std)
+        return [TensorDecl(spec.weight_name, (spec.size,), init)]
+
+    def out_args(self):
+        return (self.weight, self.eps, self.offset)
+
+    def forward(self, x, out):
+        ops.norm32(out, x, self.weight, self.eps, self.offset)
+        return out
+
+    def branch_add(self, x, delta, mult, h=None, next_norm=None):
+        out_norm = next_norm.out_args() if next_norm is not None else None
+        ops.branch_norm_add32(x, delta, self.weight, self.eps, mult, self.offset, h, out_norm)
+        return h
+
+
+class StreamCast(Norm):
+    """Stands where a block's input norm would: the block's sublayers read the 32-bit stream itself, rounded to the
+    element type of the products."""
+
+    def out_args(self):
+        return None
+
+    def forward(self, x, out):
+        ops.cast_rows(out, x)
+        return out

@@ -1,0 +1,97 @@
+"""A routed feed-forward: a router picks ``top`` of ``experts`` small gated units per token; a shared unit may run for
+every token and is added.
+
+    z = Wr h (32-bit), score = sigmoid(z); the `top` largest scores choose the experts (ties to the smaller index)
+    unit(u; limit) = Wdown( a * sigmoid(slope * a) * (b + shift) ),  a = min(Wgate u, limit),  b = clamp(Wup u, -limit, limit)
+    out = sum_chosen unit_e(score_e * h)  [+ unit_shared(h)]         with ``scale_input`` (the score scales the INPUT)
+    out = sum_chosen score_e * unit_e(h)  [+ unit_shared(h)]         without it
+
+Options of the record: ``experts``, ``top``, ``limit``, ``sigmoid_slope``, ``up_shift``, ``scale_input``, ``renormalize``
+(divide the chosen scores by their sum), ``shared_size`` / ``shared_limit`` (0: no shared unit). ``intermediate_size`` is
+an expert's size. Tensor names: ``router``, ``expert`` (a prefix pattern with ``{}`` for the expert's number), ``shared``
+(a prefix), and inside a unit ``gate``, ``up``, ``down``.
+
+On the device the (token, choice) pairs are grouped by expert and every expert's rows go through its matrices in
+tiles (``csrc/routed_experts.cu``); no count is read on the host, so a one-token step stays capturable.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..config.spec import FeedForwardSpec, TensorDecl
+from ..kernels import ops
+from .base import FeedForward, register_feed_forward
+from .linear import Linear
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts(FeedForward):
+    def __init__(self, spec: FeedForwardSpec, tensors, rt):
+        self.spec, self.rt = spec, rt
+        o, n, p = spec.options, spec.tensor_names, spec.prefix
+        self.experts, self.top = int(o["experts"]), int(o["top"])
+        self.limit = float(o["limit"])
+        self.slope, self.shift = float(o.get("sigmoid_slope", 1.0)), float(o.get("up_shift", 0.0))
+        self.scale_input = bool(o.get("scale_input", False))
+        if o.get("renormalize", False) or o.get("score", "sigmoid") != "sigmoid":
+            raise ValueError("routed_experts: only unnormalised sigmoid scores are built")
+        get = lambda name: rt.param(tensors[p + name])
+        self.router = get(n["router"])
+        units = [p + n["expert"].format(e) for e in range(self.experts)]
+        unit = lambda u, k: rt.param(tensors[u + n[k]])
+        # Every expert's gate rows then its up rows, expert after expert; the down matrices likewise.
+        self.gate_up = torch.stack([torch.cat([unit(u, "gate"), unit(u, "up")], 0) for u in units]).contiguous()
+        self.down = torch.stack([unit(u, "down") for u in units]).contiguous()
+        self.shared_size = int(o.get("shared_size", 0))
+        if self.shared_size:
+            u = p + n["shared"]
+            self.shared_limit = float(o["shared_limit"])
+            self.shared_gate_up = Linear(torch.cat([unit(u, "gate"), unit(u, "up")], 0).contiguous(), rt, "shared_gate_up")
+            self.shared_down = Linear(unit(u, "down"), rt, "shared_down")
+
+    @classmethod
+    def tensors(cls, spec: FeedForwardSpec):
+        o, n, p = spec.options, spec.tensor_names, spec.prefix
+        W, F = spec.hidden_size, spec.intermediate_size
+        std = lambda fan_in: ("normal", fan_in ** -0.5)
+        out = [TensorDecl(p + n["router"], (int(o["experts"]), W), std(W))]
+
+        def unit(u, size):
+            return [TensorDecl(u + n["gate"], (size, W), std(W)), TensorDecl(u + n["up"], (size, W), std(W)),
+                    TensorDecl(u + n["down"], (W, size), std(size))]
+        for e in range(int(o["experts"])):
+            out += unit(p + n["expert"].format(e), F)
+        if int(o.get("shared_size", 0)):
+            out += unit(p + n["shared"], int(o["shared_size"]))
+        return out
+
+    def forward(self, h, step):
+        rt, spec = self.rt, self.spec
+        n, W = h.shape
+        F, top, E = spec.intermediate_size, self.top, self.experts
+        pairs = n * top
+        ids = rt.buffer("experts.ids", (n, top), torch.int32)
+        scores = rt.buffer("experts.scores", (n, top), torch.float32)
+        ops.router_topk(h, self.router, top, ids, scores)
+        words, max_tiles = ops.expert_plan_sizes(pairs, E)
+        pair_row = rt.buffer("experts.pair_row", (pairs,), torch.int32)
+        row_pair = rt.buffer("experts.row_pair", (pairs,), torch.int32)
+        plan = rt.buffer("experts.plan", (words,), torch.int32)
+        ops.expert_plan(ids, E, pair_row, row_pair, plan)
+        shared = None
+        if self.shared_size:
+            gu = rt.buffer("experts.shared_gate_up", (n, 2 * self.shared_size))
+            self.shared_gate_up.forward(h, gu)
+            act = rt.buffer("experts.shared_act", (n, self.shared_size))
+            ops.gated_unit_limit(act, gu, self.shared_limit, self.slope, self.shift)
+            shared = rt.buffer("experts.shared_out", (n, W))
+            self.shared_down.forward(act, shared)
+        xs = rt.buffer("experts.rows", (pairs, W))
+        ops.expert_gather(xs, h, row_pair, scores, top, self.scale_input)
+        act = rt.buffer("experts.act", (pairs, F))
+        ops.grouped_gemm(act, xs, self.gate_up, plan, max_tiles, gated=True, limit=self.limit, slope=self.slope, shift=self.shift)
+        ys = rt.buffer("experts.out_rows", (pairs, W))
+        ops.grouped_gemm(ys, act, self.down, plan, max_tiles)
+        out = rt.buffer("feed_forward.delta", (n, W))
+        ops.expert_combine(out, ys, pair_row, scores, shared, top, scale_output=not self.scale_input)
+        return out
