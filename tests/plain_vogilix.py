@@ -108,18 +108,25 @@ def expert(h, W, p, limit, dtype):
     return linear(y, W[p + "down"], dtype)
 
 
-def router(x, W, p, top, dtype):
-    """(expert ids [n, top], their scores [n, top]); logits in 32-bit from the rounded input."""
+def router(x, W, p, top, dtype, margins=None):
+    """(expert ids [n, top], their scores [n, top]); logits in 32-bit from the rounded input. ``margins``: a list
+    that receives, per row, how far the last chosen logit is above the first one left out, relative to the row's
+    root mean square (a small value marks a choice that rounding could turn)."""
     z = (rnd(x, dtype).double() @ W[p + "router"].double().t()).to(F32)
-    s = torch.sigmoid(z)
-    val, idx = torch.topk(s, top, dim=-1)
-    return idx, val
+    val, idx = torch.topk(z, top, dim=-1)
+    if margins is not None:
+        if top < z.shape[1]:
+            srt = torch.sort(z, dim=-1, descending=True).values
+            margins.append((srt[:, top - 1] - srt[:, top]) / z.pow(2).mean(-1).sqrt().clamp_min(1e-30))
+        else:
+            margins.append(torch.full((z.shape[0],), float("inf")))
+    return idx, torch.sigmoid(val)
 
 
-def moe_ff(x, W, p, mlp, dtype):
+def moe_ff(x, W, p, mlp, dtype, margins=None):
     n = x.shape[0]
     r = mlp["router"]
-    idx, val = router(x, W, p, r["top"], dtype)
+    idx, val = router(x, W, p, r["top"], dtype, margins)
     h = rnd(x, dtype)
     out = torch.zeros(n, x.shape[1], dtype=torch.float64)
     for t in range(n):
@@ -140,9 +147,9 @@ def side_input(x, tokens, W, layer, i, dim, eps, dtype):
     return norm_plain(y, W[layer + "side.norm"], eps)
 
 
-def forward(cfg, W, tokens, dtype=F32, layers_out=None):
+def forward(cfg, W, tokens, dtype=F32, layers_out=None, margins=None):
     """Logits [n, vocab] of one sequence from position 0; ``layers_out``: a list that receives the residual
-    stream after every layer."""
+    stream after every layer; ``margins``: a list that receives (layer, router margins [n]) of every routed layer."""
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     n = tokens.shape[0]
     eps, m = cfg["norm"]["eps"], cfg.get("residual_mult", 1.0)
@@ -157,7 +164,13 @@ def forward(cfg, W, tokens, dtype=F32, layers_out=None):
         x = x + m * norm_offset(y, W[L + "norm1"], eps)
         mlp = layer.get("mlp")
         if mlp:
-            y = dense_ff(x, W, L + "mlp.", dtype) if mlp["kind"] == "dense" else moe_ff(x, W, L + "mlp.", mlp, dtype)
+            if mlp["kind"] == "dense":
+                y = dense_ff(x, W, L + "mlp.", dtype)
+            else:
+                got = [] if margins is not None else None
+                y = moe_ff(x, W, L + "mlp.", mlp, dtype, got)
+                if got:
+                    margins.append((i, got[0]))
             x = x + m * norm_offset(y, W[L + "norm2"], eps)
         if side:
             x = x + m * side_input(x, tokens, W, L, i, side["dim"], eps, dtype)
@@ -177,3 +190,20 @@ def load_folder(folder):
         for k in f.keys():
             W[k] = f.get_tensor(k)
     return cfg, W
+
+
+def unsure_positions(cfg, margins, n, threshold):
+    """Positions of a sequence of ``n`` tokens whose result a turned router choice could have changed: the positions
+    whose margin in some routed layer is below ``threshold``, and the later positions that can see them through the
+    attention of the layers after it (each such layer carries a change forward by its window, less one)."""
+    bad = torch.zeros(n, dtype=torch.bool)
+    by_layer = dict(margins)
+    for i, layer in enumerate(cfg["layers"]):
+        if bad.any():                                   # this layer's attention spreads what earlier layers changed
+            window = (layer["mixer"].get("mask") or {}).get("size") or n
+            idx = torch.nonzero(bad).flatten()
+            for p in idx.tolist():
+                bad[p:min(n, p + window)] = True
+        if i in by_layer:
+            bad |= by_layer[i] < threshold
+    return bad
