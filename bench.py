@@ -4,6 +4,7 @@ model with random weights (bfloat16), plus prefill throughput and roofline fract
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--dtype bfloat16|float32] [--impl reference]
     python bench.py --preset 8b-long | 70b        (the other two sizes the reference names; a line each)
+    python bench.py --preset vogilix [--timeline]  (the Vogilix design at two sizes beside Apertus layers of equal size)
 
 Prints one JSON line. A "step" is one decode step of the whole batch (default batch 8, every
 sequence after 1,023 cached positions, context 4,096). ``value`` is decoded tokens per second
@@ -369,6 +370,85 @@ def run_sweep(args, pk, pk_source):
     return 0
 
 
+# The Vogilix design at sizes that resemble a served model's layers, and Apertus layers of equal width, depth, head
+# count and feed-forward work per token beside them. "mid": width 2,048, 16 heads, a key/value latent of 128 (what the
+# cache keeps per position and layer), a window of 1,024, 32 experts of 1,024 of which 4 run per token, and a shared one.
+# "wide": width 4,096, 32 heads, a latent of 256, 64 experts of 1,408, 6 per token.
+def vogilix_config(size: str, layers: int):
+    w, heads, dim, q_rank, kv_rank, window, dense, experts, top, ff, shared, side, vocab = {
+        "mid": (2048, 16, 64, 768, 128, 1024, 8192, 32, 4, 1024, 2048, 64, 32768),
+        "wide": (4096, 32, 128, 1536, 256, 2048, 12288, 64, 6, 1408, 2816, 128, 65536)}[size]
+    mixer = {"dim": dim, "heads": heads, "kv_rank": kv_rank, "mask": {"size": window}, "q_rank": q_rank, "scale": dim ** -0.5, "vdim": dim}
+    moe = {"expert": {"ff": ff, "limit": 7.0}, "kind": "moe", "router": {"experts": experts, "top": top}, "shared": {"ff": shared, "limit": 7.0}}
+    return {"architecture": "Vogilix", "vocab": vocab, "width": w, "max_positions": 4096, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "token_side": {"dim": side},
+            "layers": [{"mixer": mixer, "mlp": {"ff": dense, "kind": "dense"} if i == 0 else moe, "type": "latent_attention"}
+                       for i in range(layers)]}
+
+
+def apertus_twin(v: dict):
+    """Apertus layers beside a Vogilix configuration: the same width, depth, heads, head size, window-free attention
+    with a quarter as many KV heads, and a feed-forward with the multiply-adds per token of the routed layers
+    (top experts + shared, three matrices each, against two)."""
+    m, moe = v["layers"][0]["mixer"], v["layers"][-1]["mlp"]
+    per_token = 3 * (moe["router"]["top"] * moe["expert"]["ff"] + moe["shared"]["ff"]) if moe["kind"] == "moe" else 2 * moe["ff"]
+    return dict(APERTUS_8B, num_hidden_layers=len(v["layers"]), hidden_size=v["width"], num_attention_heads=m["heads"],
+                num_key_value_heads=max(1, m["heads"] // 4), head_dim=m["dim"] if m["dim"] >= 64 else 64,
+                intermediate_size=per_token // 2 // 64 * 64, vocab_size=v["vocab"], max_position_embeddings=4096)
+
+
+def run_vogilix(args, pk, pk_source):
+    """Prefill and decode throughput of the Vogilix design at two sizes, each beside its Apertus twin; with --timeline
+    also the per-kernel device times of one prompt step and one decode step of the Vogilix model (stderr)."""
+    import torch
+    from tileinfer_b200.config import config_from_dict
+    from tileinfer_b200.engine import Engine
+    layers = args.layers or 8
+    steps, warmup = max(8, min(args.steps, 32)), max(args.warmup, 3)
+    clocks = ClockSampler()
+    clocks.start()
+    out = []
+    for size in ("mid", "wide"):
+        v = vogilix_config(size, layers)
+        for name, raw in (("vogilix", v), ("apertus", apertus_twin(v))):
+            cfg = config_from_dict(raw)
+            engine = Engine.random(cfg, seed=0, dtype=args.dtype, max_context=4096, max_seqs=64, max_tokens=64 * 1280,
+                                   max_step_tokens=8192)
+            row = {"size": size, "model": name, "layers": layers, "weights_gb": round(engine.weight_bytes() / 1e9, 3),
+                   "cache_bytes_per_position": engine.kv_bytes_per_position()}
+            for tokens in (512, 2048):
+                ms = time_prefill(engine, tokens, cfg.vocab_size, reps=3)
+                row[f"prefill_{tokens}_ms"] = round(ms, 3)
+                row[f"prefill_{tokens}_tok_s"] = round(tokens * 1000.0 / ms, 1)
+            for b in (1, 8, 64):
+                ms, _, launches = time_decode(engine, b, steps, warmup, cfg.vocab_size, count_launches=True)
+                row[f"decode_b{b}_ms"] = round(ms, 4)
+                row[f"decode_b{b}_tok_s"] = round(b * 1000.0 / ms, 1)
+                row[f"decode_b{b}_launches"] = launches
+            engine.check_health()
+            out.append(row)
+            del engine
+            torch.cuda.empty_cache()
+    clock_info = clocks.stop()
+    if args.timeline:
+        from tileinfer_b200.kernels import microbench
+        import contextlib
+        with contextlib.redirect_stdout(sys.stderr):
+            for size in ("mid", "wide"):
+                cfg = config_from_dict(vogilix_config(size, min(layers, 4)))
+                print(f"--- {size}: prompt of 2,048 tokens")
+                microbench.timeline(1, 0, prefill_tokens=2048, config=cfg, first=60)
+                for b in (8, 64):
+                    print(f"--- {size}: decode step of batch {b}")
+                    microbench.timeline(b, 0, config=cfg, first=60 if b == 8 else 1)
+    print(json.dumps({"metric": "prefill and decode of the Vogilix design beside Apertus layers of equal size", "n_gpus": 1,
+                      "steps": steps, "warmup": warmup, "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
+                      "data": "synthetic: random weights, uniform random token ids",
+                      "config": {"cached_positions": CACHED, "peaks": pk_source, "l2": "every step reads more weights than L2 holds"},
+                      "clocks": clock_info, "rows": out}))
+    return 0
+
+
 def flops_prefill(cfg, n_layers, tokens):
     H, I, D = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
     nq, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
@@ -396,7 +476,8 @@ def main(argv=None) -> int:
                     help="float32: the true 32-bit path (strict 32-bit FMA products) as the headline")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (quick checks)")
-    ap.add_argument("--preset", default="8b", choices=["8b", "8b-long", "70b", "sweep"],
+    ap.add_argument("--timeline", action="store_true", help="--preset vogilix: per-kernel device times of its steps, on stderr")
+    ap.add_argument("--preset", default="8b", choices=["8b", "8b-long", "70b", "sweep", "vogilix"],
                     help="8b: the headline line (default); 8b-long: 8 unequal sequences of up to 32,768 positions; "
                          "70b: Apertus-70B sizes, 141 GB of weights")
     args = ap.parse_args(argv)
@@ -420,6 +501,8 @@ def main(argv=None) -> int:
         return run_70b(args, *peaks())
     if args.preset == "sweep":
         return run_sweep(args, *peaks())
+    if args.preset == "vogilix":
+        return run_vogilix(args, *peaks())
     cfg_dict = dict(APERTUS_8B)
     full_layers = cfg_dict["num_hidden_layers"]
     if args.layers:

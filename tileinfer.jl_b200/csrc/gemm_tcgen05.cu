@@ -51,6 +51,14 @@ struct Params {
     int* status;
     int tma_out;                   // bfloat16 results leave through shared memory and TMA stores
     int rotate;                    // every weight tile starts at another place of its k range
+    // Many matrices in one launch. Grouped by token tile (one matrix per expert): `groups` is a device table,
+    // [0] = token tiles in use (at most n_tiles), [1 + n] = the matrix of token tile n; matrix g starts at weight row
+    // g * w_group_rows. Batched (one matrix per head, all tokens): `batch` matrices, matrix b starts at weight row
+    // b * w_batch_rows, reads the tokens' columns from b * x_batch_k on and writes the columns from b * y_batch_cols on.
+    const int* groups;
+    int w_group_rows;
+    int batch, w_batch_rows, x_batch_k;
+    long long y_batch_cols;
 };
 
 // MT: 128-row weight sub-tiles per block. With MT = 2 a block owns 256 weight rows: the token
@@ -81,13 +89,14 @@ template <int BN> __device__ __forceinline__ constexpr unsigned instr_desc() {
 }
 
 struct TileIter {
-    int id, step, total;
-    int m, n, kb_lo, kb_hi, split, rot;
+    int id, step, total, n_tiles;
+    int m, n, b, kb_lo, kb_hi, split, rot;
     __device__ bool next(const Params& p) {
         if (id >= total) return false;
         int t = id;
-        n = t % p.n_tiles; t /= p.n_tiles;
-        split = t % p.splits; m = t / p.splits;
+        n = t % n_tiles; t /= n_tiles;
+        split = t % p.splits; t /= p.splits;
+        m = t % p.m_tiles; b = t / p.m_tiles;
         kb_lo = (int)((long long)p.k_blocks * split / p.splits);
         kb_hi = (int)((long long)p.k_blocks * (split + 1) / p.splits);
         rot = p.rotate ? (m * 7) % (kb_hi - kb_lo) : 0;
@@ -102,7 +111,7 @@ struct TileIter {
 template <int BN, int EPI_WARPS, int OUT_BYTES>
 __device__ __forceinline__ void epilogue_rows(unsigned t_row, int m_first, int lane, int n0, int n_valid, int col_group, int warp_slot,
                                               int split, int& out_buf, unsigned char* out_tiles, const CUtensorMap* map_y, void* y,
-                                              const Params& p, const XieluPacked& act) {
+                                              const Params& p, const XieluPacked& act, long long y_col0 = 0) {
     constexpr int CH = BN >= 32 ? 32 : 16;
     const int m = m_first + lane;
 #pragma unroll 1
@@ -115,7 +124,7 @@ __device__ __forceinline__ void epilogue_rows(unsigned t_row, int m_first, int l
         // independent elements in flight hide the latency of the arithmetic), then the stores.
         if (p.epilogue >= EPI_F32) {
             if (m < p.M) {
-                float* yf = (float*)y + ((size_t)(p.epilogue == EPI_PARTIAL ? split : 0) * p.N + n0 + c) * p.ldy + m;
+                float* yf = (float*)y + ((size_t)(p.epilogue == EPI_PARTIAL ? split : 0) * p.N + n0 + c) * p.ldy + y_col0 + m;
 #pragma unroll
                 for (int j = 0; j < CH; ++j) {
                     const float s = __uint_as_float(r[j]);
@@ -148,10 +157,10 @@ __device__ __forceinline__ void epilogue_rows(unsigned t_row, int m_first, int l
                 reinterpret_cast<unsigned short*>(tile)[j * 32 + lane] = (unsigned short)o[j];
             fence_async_smem();
             __syncwarp();
-            if (lane == 0 && m_first < p.M) tma_store_2d(map_y, smem_addr(tile), m_first, n0 + c);
+            if (lane == 0 && m_first < p.M) tma_store_2d(map_y, smem_addr(tile), (int)y_col0 + m_first, n0 + c);
             out_buf ^= 1;
         } else if (m < p.M) {
-            unsigned short* yb = (unsigned short*)y + (size_t)(n0 + c) * p.ldy + m;
+            unsigned short* yb = (unsigned short*)y + (size_t)(n0 + c) * p.ldy + y_col0 + m;
 #pragma unroll
             for (int j = 0; j < CH; ++j)
                 if (c + j < n_valid) yb[(size_t)j * p.ldy] = (unsigned short)o[j];
@@ -187,14 +196,14 @@ __global__ void __launch_bounds__(Cfg<BN, MT>::THREADS, Cfg<BN, MT>::BLOCKS_PER_
     __syncthreads();
     tc_fence_after();
     TileIter it;
-    it.id = blockIdx.x; it.step = gridDim.x; it.total = p.m_tiles * p.n_tiles * p.splits;
+    it.id = blockIdx.x; it.step = gridDim.x; it.n_tiles = p.n_tiles; it.total = p.m_tiles * p.n_tiles * p.splits * p.batch;
 
     // Barriers and tensor memory are set up while the previous kernel drains, and the weights do not
     // depend on it: the loads of the first tile's first weight blocks (as many as the pipeline has
     // stages) are on their way before the wait. The previous kernel's results (the activations, and the
-    // output buffer it may still read) are touched only after it.
+    // output buffer it may still read) are touched only after it. (Not with a table of groups, which is such a result.)
     int ahead = 0;
-    if (warp == 0) {
+    if (warp == 0 && p.groups == nullptr) {
         TileIter first = it;
         if (first.next(p)) {
             ahead = min(C::STAGES, first.kb_hi - first.kb_lo);
@@ -205,13 +214,17 @@ __global__ void __launch_bounds__(Cfg<BN, MT>::THREADS, Cfg<BN, MT>::BLOCKS_PER_
                     const unsigned a_dst = smem_addr(tiles + (size_t)s * C::STAGE_BYTES);
 #pragma unroll
                     for (int h = 0; h < MT; ++h)
-                        tma_load_2d(a_dst + h * (BM * BK * 2), &map_w, first.kb_at(s) * BK, (first.m * MT + h) * BM, bar);
+                        tma_load_2d(a_dst + h * (BM * BK * 2), &map_w, first.kb_at(s) * BK, first.b * p.w_batch_rows + (first.m * MT + h) * BM, bar);
                 }
             __syncwarp();
         }
     }
     pdl_wait();
     pdl_launch_dependents();
+    if (p.groups != nullptr) {
+        it.n_tiles = min(__ldcg(p.groups), p.n_tiles);
+        it.total = p.m_tiles * it.n_tiles * p.splits * p.batch;
+    }
     const unsigned tmem_base = *tmem_slot;
 
     if (warp == 0) {
@@ -231,11 +244,12 @@ __global__ void __launch_bounds__(Cfg<BN, MT>::THREADS, Cfg<BN, MT>::BLOCKS_PER_
                 const unsigned a_dst = smem_addr(tiles + (size_t)stage * C::STAGE_BYTES);
                 if (issued >= ahead) {                      // else the weights of this stage are already on their way
                     mbar_expect_tx(bar, C::STAGE_BYTES);
+                    const int w_row = it.b * p.w_batch_rows + (p.groups != nullptr ? __ldcg(p.groups + 1 + it.n) * p.w_group_rows : 0);
 #pragma unroll
                     for (int h = 0; h < MT; ++h)
-                        tma_load_2d(a_dst + h * (BM * BK * 2), &map_w, kb * BK, (it.m * MT + h) * BM, bar);
+                        tma_load_2d(a_dst + h * (BM * BK * 2), &map_w, kb * BK, w_row + (it.m * MT + h) * BM, bar);
                 }
-                tma_load_2d(a_dst + C::A_BYTES, &map_x, kb * BK, it.n * BN, bar);
+                tma_load_2d(a_dst + C::A_BYTES, &map_x, it.b * p.x_batch_k + kb * BK, it.n * BN, bar);
                 if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
             }
         }
@@ -291,7 +305,7 @@ __global__ void __launch_bounds__(Cfg<BN, MT>::THREADS, Cfg<BN, MT>::BLOCKS_PER_
             const int m_first = (it.m * MT + h) * BM + quarter * 32;
             const unsigned t_row = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)((acc * MT + h) * BN);
             epilogue_rows<BN, C::EPI_WARPS, C::OUT_BYTES>(t_row, m_first, lane, n0, n_valid, col_group, warp - 2, it.split, out_buf,
-                                                          out_tiles, &map_y, y, p, act);
+                                                          out_tiles, &map_y, y, p, act, it.b * p.y_batch_cols);
             }
             tc_fence_before();
             __syncwarp();
@@ -409,7 +423,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
     const unsigned tmem_base = *tmem_slot;
 
     TileIter it;
-    it.id = blockIdx.x >> 1; it.step = gridDim.x >> 1; it.total = p.m_tiles * p.n_tiles * p.splits;
+    it.id = blockIdx.x >> 1; it.step = gridDim.x >> 1; it.n_tiles = p.n_tiles; it.total = p.m_tiles * p.n_tiles * p.splits;
 
     if (warp == 0) {
         // ---------------------------------------------------------------- producer (TMA), in both blocks
@@ -519,7 +533,7 @@ int launch(void* y, const CUtensorMap& mw, const CUtensorMap& mx, const CUtensor
         if (e != cudaSuccess) return ti_fail("gemm_tcgen05: %s", cudaGetErrorString(e));
         configured = true;
     }
-    const int tiles = p.m_tiles * p.n_tiles * p.splits;
+    const int tiles = p.m_tiles * p.n_tiles * p.splits * p.batch;
     const int slots = sm_count * Cfg<BN, MT>::BLOCKS_PER_SM;
     const int grid = tiles < slots ? tiles : slots;
     ti_launch(gemm_tcgen05_kernel<BN, MT>, dim3(grid), dim3(Cfg<BN, MT>::THREADS), Cfg<BN, MT>::SMEM, stream, mw, mx, my, y, p);
@@ -558,6 +572,7 @@ int gemm_dispatch(void* y, long long ldy, const void* x, long long ldx, const vo
     const int bn = n > 128 ? 256 : n > 64 ? 128 : n > 32 ? 64 : 32;
     Params p;
     p.N = n; p.K = in;
+    p.groups = nullptr; p.w_group_rows = 0; p.batch = 1; p.w_batch_rows = 0; p.x_batch_k = 0; p.y_batch_cols = 0;
     // Wide token tiles (more than 128 tokens): two SMs share a tile of 256 weight rows x 256 tokens
     // (cta_group::2): per MMA each SM fills 32 KB of shared memory instead of 48 KB, both accumulator buffers
     // stay, so the epilogue (xIELU included) overlaps the next tile, and a stage of 128 of k means one barrier
@@ -605,7 +620,81 @@ int gemm_dispatch(void* y, long long ldy, const void* x, long long ldx, const vo
     }
 }
 
+int sm_count_cached() {
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (sm_count <= 0) sm_count = 148;
+    }
+    return sm_count;
+}
+
+// Many matrices in one launch of the one-block-per-tile kernel, bfloat16 out. `bn`: tokens per tile.
+int many_dispatch(void* y, long long ldy, const void* x, long long ldx, const void* W, long long w_rows, int n, int out, int in, int bn,
+                  Params p, int* status, cudaStream_t stream) {
+    p.N = n; p.K = in; p.M = out;
+    p.m_tiles = (out + BM - 1) / BM;
+    p.n_tiles = (n + bn - 1) / bn;
+    p.k_blocks = (in + BK - 1) / BK;
+    p.splits = 1;
+    p.ldy = ldy; p.epilogue = EPI_NONE; p.act = XieluParams{0.f, 0.f, 0.f, 0.f}; p.status = status;
+    p.rotate = bn <= 64;
+    CUtensorMap mw, mx, my;
+    if (int rc = tensor_map(&mw, W, w_rows, in, in, BM)) return rc;
+    if (int rc = tensor_map(&mx, x, n, ldx, ldx, bn)) return rc;          // all columns of the rows: a batch picks its own
+    // Results leave by TMA stores in boxes of 32 features: a box must lie within one matrix's columns.
+    p.tma_out = bn >= 128 && out % 32 == 0 && ldy % 8 == 0 && !((uintptr_t)y & 15);
+    if (p.tma_out) {
+        if (int rc = tensor_map(&my, y, n, ldy, ldy, 32, 32)) return rc;
+    } else {
+        my = mx;
+    }
+    const int sms = sm_count_cached();
+    switch (bn) {
+        case 256: return launch<256, 1>(y, mw, mx, my, p, sms, stream);
+        case 128: return launch<128, 1>(y, mw, mx, my, p, sms, stream);
+        case 64: return launch<64, 1>(y, mw, mx, my, p, sms, stream);
+        case 32: return launch<32, 1>(y, mw, mx, my, p, sms, stream);
+        default: return ti_fail("gemm_tcgen05: token tiles of %d", bn);
+    }
+}
+
 }  // namespace
+
+// Rows of x grouped by matrix in token tiles of `tile` rows (32, 64, 128 or 256): y[row, :] = W[g(row)] x[row, :], W
+// [matrices, out, in]. `groups` (device): [0] = tiles in use, [1 + t] = the matrix of tile t; `rows` = the rows that x and
+// y hold (a multiple of `tile`, the capacity: tiles beyond groups[0] are not touched). Returns 2 for sizes it refuses.
+extern "C" int ti_gemm_tcgen05_grouped(void* y, const void* x, const void* W, const int* groups, int rows, int tile, int matrices,
+                                       int out, int in, int* status, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    if (in % 8 != 0 || out % 8 != 0 || in < 8 || ((uintptr_t)W & 15) || ((uintptr_t)x & 15) || ((uintptr_t)y & 15) || rows % tile != 0 ||
+        (tile != 32 && tile != 64 && tile != 128 && tile != 256) || (long long)matrices * out > 0x7fffffffLL) {
+        ti_fail("gemm_tcgen05_grouped needs 16-byte aligned rows and tiles of 32 to 256 rows: in=%d, out=%d, rows=%d, tile=%d", in, out, rows, tile);
+        return 2;
+    }
+    TI_REQUIRE(status != nullptr && groups != nullptr, "gemm_tcgen05_grouped: status word or group table missing");
+    Params p;
+    p.groups = groups; p.w_group_rows = out; p.batch = 1; p.w_batch_rows = 0; p.x_batch_k = 0; p.y_batch_cols = 0;
+    return many_dispatch(y, out, x, in, W, (long long)matrices * out, rows, out, in, tile, p, status, stream);
+}
+
+// One matrix per head over all tokens: y[t, h, :] = W[h] x[t, h, :], W [heads, out_h, in_h], x [n, heads * in_h],
+// y [n, heads * out_h]. Returns 2 for sizes it refuses.
+extern "C" int ti_gemm_tcgen05_heads(void* y, const void* x, const void* W, int n, int heads, int out_h, int in_h, int* status,
+                                     cudaStream_t stream) {
+    if (n == 0) return 0;
+    if (in_h % 8 != 0 || out_h % 8 != 0 || in_h < 8 || ((uintptr_t)W & 15) || ((uintptr_t)x & 15) || ((uintptr_t)y & 15)) {
+        ti_fail("gemm_tcgen05_heads needs 16-byte aligned rows: in=%d, out=%d", in_h, out_h);
+        return 2;
+    }
+    TI_REQUIRE(status != nullptr, "gemm_tcgen05_heads: status word missing");
+    Params p;
+    p.groups = nullptr; p.w_group_rows = 0; p.batch = heads; p.w_batch_rows = out_h; p.x_batch_k = in_h; p.y_batch_cols = out_h;
+    const int bn = n > 128 ? 256 : n > 64 ? 128 : n > 32 ? 64 : 32;
+    return many_dispatch(y, (long long)heads * out_h, x, (long long)heads * in_h, W, (long long)heads * out_h, n, out_h, in_h, bn, p, status, stream);
+}
 
 // y: [n, ldy] bfloat16 (float32 for EPI_F32), or partial sums [splits, n, ldy] float32 for EPI_PARTIAL.
 // `status` is a device word that must be zero; a non-zero value afterwards means a wait ran out.

@@ -2,11 +2,13 @@
 //
 //   router_topk     z = Wr h in 32-bit (one warp per expert and token, lanes stride over the width), score = sigmoid(z);
 //                   the `top` largest (ties to the smaller index) -> ids [n, top], scores [n, top]
-//   expert_plan     the (token, choice) pairs grouped by expert: a row for every pair in expert order, and the list of
-//                   row tiles (expert, first row, rows) that the grouped products walk; one block, counts in shared memory
-//   expert_gather   xs[row] = T(score * h[token]) (the score scales an expert's INPUT) or T(h[token])
-//   grouped_gemm    for every tile: y[row, :] = W[expert] xs[row, :]; as a gated unit W[expert] holds gate rows then up
-//                   rows and y = a * sigmoid(slope * a) * (b + shift), a = min(gate, limit), b = clamp(up, -limit, limit)
+//   expert_plan     the (token, choice) pairs grouped by expert: a row for every pair in expert order, every expert's rows
+//                   padded to whole tiles, and the expert of every tile; one block, counts in shared memory
+//   expert_gather   xs[row] = T(score * h[token]) (the score scales an expert's INPUT) or T(h[token]); zeros in padding rows
+//   grouped_gemm    for every tile: y[row, :] = W[expert] xs[row, :] on the CUDA cores (the 32-bit path, and sizes the
+//                   tensor-core kernel refuses; csrc/gemm_tcgen05.cu has the tensor-core form); as a gated unit W[expert]
+//                   holds gate rows then up rows and y = a * sigmoid(slope * a) * (b + shift), a = min(gate, limit),
+//                   b = clamp(up, -limit, limit)
 //   expert_combine  out[token] = sum over the token's choices, in choice order, of y[row(token, choice)] (times the score
 //                   where it scales the OUTPUT) + the shared unit's row, in 32-bit, rounded once
 //
@@ -20,18 +22,22 @@
 #define RT_MAX_EXPERTS 1024
 
 template <typename T>
-__global__ void router_topk_kernel(const T* h, const T* __restrict__ wr, int width, int experts, int top, int* __restrict__ ids,
-                                   float* __restrict__ scores) {
+__global__ void router_topk_kernel(const T* h, const T* __restrict__ wr, const float* logits, int width, int experts, int top,
+                                   int* __restrict__ ids, float* __restrict__ scores) {
     __shared__ float z[RT_MAX_EXPERTS];
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     pdl_enter();
-    const T* row = h + (size_t)t * width;
-    for (int e = warp; e < experts; e += RT_THREADS / 32) {
-        const T* w = wr + (size_t)e * width;
-        float a = 0.f;
-        for (int i = lane; i < width; i += 32) a = fmaf(to_f32(__ldcg(row + i)), to_f32(w[i]), a);
-        a = warp_sum(a);
-        if (lane == 0) z[e] = a;
+    if (logits != nullptr) {                               // a product kernel has left the 32-bit sums
+        for (int e = threadIdx.x; e < experts; e += RT_THREADS) z[e] = __ldcg(logits + (size_t)t * experts + e);
+    } else {
+        const T* row = h + (size_t)t * width;
+        for (int e = warp; e < experts; e += RT_THREADS / 32) {
+            const T* w = wr + (size_t)e * width;
+            float a = 0.f;
+            for (int i = lane; i < width; i += 32) a = fmaf(to_f32(__ldcg(row + i)), to_f32(w[i]), a);
+            a = warp_sum(a);
+            if (lane == 0) z[e] = a;
+        }
     }
     __syncthreads();
     if (warp == 0) {
@@ -57,44 +63,38 @@ __global__ void router_topk_kernel(const T* h, const T* __restrict__ wr, int wid
     }
 }
 
-extern "C" int ti_router_topk(const void* h, const void* wr, int n, int width, int experts, int top, int* ids, float* scores, int dtype,
-                              cudaStream_t stream) {
+// `logits` [n, experts]: the router's 32-bit sums if a product kernel has computed them (h and wr are then not read), else null.
+extern "C" int ti_router_topk(const void* h, const void* wr, const float* logits, int n, int width, int experts, int top, int* ids,
+                              float* scores, int dtype, cudaStream_t stream) {
     if (n == 0) return 0;
     TI_REQUIRE(experts >= 1 && experts <= RT_MAX_EXPERTS && top >= 1 && top <= experts, "router_topk: top %d of %d experts", top, experts);
-    TI_DISPATCH_DTYPE(dtype, (ti_launch(router_topk_kernel<T>, dim3(n), dim3(RT_THREADS), 0, stream, (const T*)h, (const T*)wr, width, experts,
-                                        top, ids, scores)));
+    TI_DISPATCH_DTYPE(dtype, (ti_launch(router_topk_kernel<T>, dim3(n), dim3(RT_THREADS), 0, stream, (const T*)h, (const T*)wr, logits, width,
+                                        experts, top, ids, scores)));
     return ti_check_launch("router_topk");
 }
 
-// plan: [0] number of tiles, [1 .. 1 + experts] first row of every expert (and the total), then tiles of 3 words.
-__global__ void expert_plan_kernel(const int* ids, int pairs, int experts, int* __restrict__ pair_row, int* __restrict__ row_pair,
-                                   int* __restrict__ plan) {
-    __shared__ int count[RT_MAX_EXPERTS], first[RT_MAX_EXPERTS + 1];
+// The plan of a step: the pairs grouped by expert, every expert's rows padded to whole tiles of `tile` rows, so that a
+// tile holds rows of one expert only (tensor-core kernels then treat a tile like any other; padding rows hold zeros and
+// nobody reads their results). plan[0] = tiles in use, plan[1 + t] = the expert of tile t. pair_row[pair] = the pair's
+// row; row_pair[row] = the row's pair, or -1 for padding, for all `capacity` rows.
+__global__ void expert_plan_kernel(const int* ids, int pairs, int experts, int tile, int capacity, int* __restrict__ pair_row,
+                                   int* __restrict__ row_pair, int* __restrict__ plan) {
+    __shared__ int count[RT_MAX_EXPERTS], first[RT_MAX_EXPERTS];
     pdl_enter();
     for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+    for (int r = threadIdx.x; r < capacity; r += blockDim.x) row_pair[r] = -1;
     __syncthreads();
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&count[__ldcg(ids + p)], 1);
     __syncthreads();
     if (threadIdx.x == 0) {
-        int at = 0, tiles = 0;
-        int* tile = plan + 2 + experts;
+        int tiles = 0;
         for (int e = 0; e < experts; ++e) {
-            first[e] = at;
-            plan[1 + e] = at;
-            for (int r = 0; r < count[e]; r += TG_ROWS) {
-                tile[3 * tiles] = e;
-                tile[3 * tiles + 1] = at + r;
-                tile[3 * tiles + 2] = min(TG_ROWS, count[e] - r);
-                ++tiles;
-            }
-            at += count[e];
+            first[e] = tiles * tile;
+            for (int r = 0; r < count[e]; r += tile) plan[1 + tiles++] = e;
+            count[e] = 0;
         }
-        first[experts] = at;
-        plan[1 + experts] = at;
         plan[0] = tiles;
     }
-    __syncthreads();
-    for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
     __syncthreads();
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
         const int e = __ldcg(ids + p);
@@ -104,16 +104,21 @@ __global__ void expert_plan_kernel(const int* ids, int pairs, int experts, int* 
     }
 }
 
-extern "C" int ti_expert_plan_words(int pairs, int experts) { return 2 + experts + 3 * (pairs < (pairs + TG_ROWS - 1) / TG_ROWS + experts ? pairs : (pairs + TG_ROWS - 1) / TG_ROWS + experts); }
-extern "C" int ti_expert_plan_max_tiles(int pairs, int experts) {
-    const int by_rows = (pairs + TG_ROWS - 1) / TG_ROWS + experts;
+// The most tiles of `tile` rows that `pairs` pairs over `experts` experts can take: every tile holds at least one pair, and
+// at most one tile per expert is not full.
+extern "C" int ti_expert_plan_max_tiles(int pairs, int experts, int tile) {
+    const int by_rows = pairs / tile + experts;
     return pairs < by_rows ? pairs : by_rows;
 }
 
-extern "C" int ti_expert_plan(const int* ids, int pairs, int experts, int* pair_row, int* row_pair, int* plan, cudaStream_t stream) {
+extern "C" int ti_expert_plan(const int* ids, int pairs, int experts, int tile, int capacity, int* pair_row, int* row_pair, int* plan,
+                              cudaStream_t stream) {
     if (pairs == 0) return 0;
     TI_REQUIRE(experts >= 1 && experts <= RT_MAX_EXPERTS, "expert_plan: %d experts", experts);
-    ti_launch(expert_plan_kernel, dim3(1), dim3(pairs >= 1024 ? 1024 : 256), 0, stream, ids, pairs, experts, pair_row, row_pair, plan);
+    TI_REQUIRE(tile >= TG_ROWS && tile % TG_ROWS == 0 && capacity == ti_expert_plan_max_tiles(pairs, experts, tile) * tile,
+               "expert_plan: tiles of %d rows, capacity %d", tile, capacity);
+    ti_launch(expert_plan_kernel, dim3(1), dim3(pairs >= 1024 ? 1024 : 256), 0, stream, ids, pairs, experts, tile, capacity, pair_row,
+              row_pair, plan);
     return ti_check_launch("expert_plan");
 }
 
@@ -123,28 +128,34 @@ __global__ void expert_gather_kernel(T* __restrict__ xs, const T* h, const int* 
     const int row = blockIdx.x;
     pdl_enter();
     const int p = __ldcg(row_pair + row);
+    T* dst = xs + (size_t)row * width;
+    if (p < 0) {                                            // a padding row
+        for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_f32<T>(0.f);
+        return;
+    }
     const float s = scale_input ? __ldcg(scores + p) : 1.0f;
     const T* src = h + (size_t)(p / top) * width;
-    T* dst = xs + (size_t)row * width;
     for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_f32<T>(s * to_f32(__ldcg(src + i)));
 }
 
-extern "C" int ti_expert_gather(void* xs, const void* h, const int* row_pair, const float* scores, int pairs, int top, int width,
+extern "C" int ti_expert_gather(void* xs, const void* h, const int* row_pair, const float* scores, int rows, int top, int width,
                                 int scale_input, int dtype, cudaStream_t stream) {
-    if (pairs == 0) return 0;
-    TI_DISPATCH_DTYPE(dtype, (ti_launch(expert_gather_kernel<T>, dim3(pairs), dim3(width >= 1024 ? 256 : 128), 0, stream, (T*)xs, (const T*)h,
+    if (rows == 0) return 0;
+    TI_DISPATCH_DTYPE(dtype, (ti_launch(expert_gather_kernel<T>, dim3(rows), dim3(width >= 1024 ? 256 : 128), 0, stream, (T*)xs, (const T*)h,
                                         row_pair, scores, top, width, scale_input)));
     return ti_check_launch("expert_gather");
 }
 
+// The grouped product on the CUDA cores: block (x, y) computes rows [32 x, 32 x + 32) x columns [64 y, 64 y + 64) with the
+// matrix of the plan's tile that holds those rows.
 template <typename T, bool GATED>
 __global__ void __launch_bounds__(TG_THREADS) grouped_gemm_kernel(T* __restrict__ y, const T* x, const T* __restrict__ w, const int* plan,
-                                                                  int experts, int out, int in, float limit, float slope, float shift) {
+                                                                  int tile, int out, int in, float limit, float slope, float shift) {
     __shared__ TileGemmSmem s;
     pdl_enter();
-    if ((int)blockIdx.x >= __ldcg(plan)) return;
-    const int* tile = plan + 2 + experts + 3 * blockIdx.x;
-    const int e = __ldcg(tile), row0 = __ldcg(tile + 1), rows = __ldcg(tile + 2);
+    const int row0 = blockIdx.x * TG_ROWS, t = row0 / tile;
+    if (t >= __ldcg(plan)) return;
+    const int e = __ldcg(plan + 1 + t), rows = TG_ROWS;
     const int col0 = blockIdx.y * TG_COLS, cols = min(TG_COLS, out - col0);
     const T* xb = x + (size_t)row0 * in;
     auto xrow = [&](int r) { return xb + (size_t)r * in; };
@@ -156,7 +167,6 @@ __global__ void __launch_bounds__(TG_THREADS) grouped_gemm_kernel(T* __restrict_
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int r = 2 * ty + i;
-        if (r >= rows) continue;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int c = tx + 16 * j;
@@ -172,14 +182,14 @@ __global__ void __launch_bounds__(TG_THREADS) grouped_gemm_kernel(T* __restrict_
     }
 }
 
-extern "C" int ti_grouped_gemm(void* y, const void* x, const void* w, const int* plan, int max_tiles, int experts, int out, int in,
+extern "C" int ti_grouped_gemm(void* y, const void* x, const void* w, const int* plan, int rows, int tile, int out, int in,
                                int gated, float limit, float slope, float shift, int dtype, cudaStream_t stream) {
-    if (max_tiles == 0) return 0;
-    TI_REQUIRE(out > 0 && in > 0 && experts > 0, "grouped_gemm: bad sizes out=%d in=%d experts=%d", out, in, experts);
-    const dim3 grid(max_tiles, (out + TG_COLS - 1) / TG_COLS);
+    if (rows == 0) return 0;
+    TI_REQUIRE(out > 0 && in > 0 && tile % TG_ROWS == 0 && rows % tile == 0, "grouped_gemm: bad sizes out=%d in=%d rows=%d tile=%d", out, in, rows, tile);
+    const dim3 grid(rows / TG_ROWS, (out + TG_COLS - 1) / TG_COLS);
     TI_DISPATCH_DTYPE(dtype, {
-        if (gated) ti_launch(grouped_gemm_kernel<T, true>, grid, dim3(TG_THREADS), 0, stream, (T*)y, (const T*)x, (const T*)w, plan, experts, out, in, limit, slope, shift);
-        else ti_launch(grouped_gemm_kernel<T, false>, grid, dim3(TG_THREADS), 0, stream, (T*)y, (const T*)x, (const T*)w, plan, experts, out, in, limit, slope, shift);
+        if (gated) ti_launch(grouped_gemm_kernel<T, true>, grid, dim3(TG_THREADS), 0, stream, (T*)y, (const T*)x, (const T*)w, plan, tile, out, in, limit, slope, shift);
+        else ti_launch(grouped_gemm_kernel<T, false>, grid, dim3(TG_THREADS), 0, stream, (T*)y, (const T*)x, (const T*)w, plan, tile, out, in, limit, slope, shift);
     });
     return ti_check_launch("grouped_gemm");
 }

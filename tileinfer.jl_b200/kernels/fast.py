@@ -178,6 +178,59 @@ def _tcgen05(lin, x, out, epilogue, act, allow_partials):
     return out
 
 
+def linear_f32(lin, x, out):
+    """The unrounded 32-bit sums x Wᵀ into ``out`` [n, out_features] float32 (a router's logits), or None when no fast
+    kernel takes these sizes. The kernels' partial-sum epilogue with one slice of k leaves exactly that."""
+    n, k = x.shape
+    w = lin.weight
+    if x.dtype != torch.bfloat16 or n == 0 or k % 8 or x.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16:
+        return None
+    if n <= GEMV_MAX_TOKENS:
+        check(lib().ti_gemv_bf16(out.data_ptr(), lin.out_features, x.data_ptr(), x.stride(0), w.data_ptr(), n, lin.out_features, k, 1, 3,
+                                 0.0, 0.0, 0.0, 0.0, _stream()), "gemv_bf16")
+        return out
+    rc = lib().ti_gemm_tcgen05(out.data_ptr(), lin.out_features, x.data_ptr(), x.stride(0), w.data_ptr(), n, lin.out_features, k, 1, 3,
+                               0.0, 0.0, 0.0, 0.0, status_word().data_ptr(), _stream())
+    if rc == 2:
+        return None
+    check(rc, "gemm_tcgen05")
+    return out
+
+
+def grouped_tile(pairs: int, experts: int) -> int:
+    """Rows per tile of the grouped products: as wide as an expert's share of the pairs fills (a tile holds one expert's
+    rows only, so wider tiles than that are padding), 32 to 128."""
+    share = pairs // max(1, experts)
+    return 128 if share >= 96 else 64 if share >= 40 else 32
+
+
+def grouped_linear(y, x, w, plan, tile) -> bool:
+    """y[row] = w[expert of the row's tile] x[row] on the tensor cores; False when the sizes are outside what the kernel
+    takes (w [experts, out, in] bfloat16)."""
+    if x.dtype != torch.bfloat16:
+        return False
+    experts, out, k = w.shape
+    rc = lib().ti_gemm_tcgen05_grouped(y.data_ptr(), x.data_ptr(), w.data_ptr(), plan.data_ptr(), x.shape[0], tile, experts, out, k,
+                                       status_word().data_ptr(), _stream())
+    if rc == 2:
+        return False
+    check(rc, "gemm_tcgen05_grouped")
+    return True
+
+
+def head_linear(y, x, w) -> bool:
+    """y[t, h, :] = w[h] x[t, h, :] on the tensor cores (w [heads, out_h, in_h] bfloat16); False for sizes it refuses."""
+    if x.dtype != torch.bfloat16:
+        return False
+    heads, out_h, in_h = w.shape
+    rc = lib().ti_gemm_tcgen05_heads(y.data_ptr(), x.data_ptr(), w.data_ptr(), x.shape[0], heads, out_h, in_h, status_word().data_ptr(),
+                                     _stream())
+    if rc == 2:
+        return False
+    check(rc, "gemm_tcgen05_heads")
+    return True
+
+
 MAX_PARTS = 32              # parts of one sequence in decode attention (the combine kernel's limit)
 
 

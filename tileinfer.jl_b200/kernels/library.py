@@ -113,10 +113,8 @@ def lib():
     wrapped.ti_sampling_uniform = handle.ti_sampling_uniform
     wrapped.ti_argmax_chunks = handle.ti_argmax_chunks
     wrapped.ti_gemm_tcgen05_decode_plan = handle.ti_gemm_tcgen05_decode_plan
-    for name in ("ti_expert_plan_words", "ti_expert_plan_max_tiles"):
-        fn = getattr(handle, name)
-        fn.restype, fn.argtypes = c_int, [c_int, c_int]
-        setattr(wrapped, name, fn)
+    handle.ti_expert_plan_max_tiles.restype, handle.ti_expert_plan_max_tiles.argtypes = c_int, [c_int, c_int, c_int]
+    wrapped.ti_expert_plan_max_tiles = handle.ti_expert_plan_max_tiles
     wrapped.handle = handle
     for name, args in _SIGNATURES.items():
         fn = getattr(handle, name)
@@ -170,9 +168,11 @@ _SIGNATURES.update({
     "ti_gelu": [_P, _P, _L, _I, _I, _P],
     "ti_gated_token_embedding": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "ti_gated_unit_limit": [_P, _P, _I, _I, _F, _F, _F, _I, _P],
-    "ti_router_topk": [_P, _P, _I, _I, _I, _I, _P, _P, _I, _P],
-    "ti_expert_plan": [_P, _I, _I, _P, _P, _P, _P],
+    "ti_router_topk": [_P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P],
+    "ti_expert_plan": [_P, _I, _I, _I, _I, _P, _P, _P, _P],
     "ti_expert_gather": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "ti_grouped_gemm": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _F, _I, _P],
+    "ti_gemm_tcgen05_grouped": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+    "ti_gemm_tcgen05_heads": [_P, _P, _P, _I, _I, _I, _I, _P, _P],
     "ti_expert_combine": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
 })

@@ -233,17 +233,23 @@ def bench_sampling(batch, vocab, once):
         print("launched 3 kernels of each kind")
 
 
-def timeline(batch, layers, cached=1023, prefill_tokens=0, shape=None):
+def timeline(batch, layers, cached=1023, prefill_tokens=0, shape=None, config=None, first=0):
+    """Per-kernel device times of one step (CUPTI through torch.profiler). ``config``: a typed configuration of any
+    registered architecture instead of Apertus layers of ``shape``; ``first``: how many kernels to list one by one
+    (default: the first Apertus layer's). Returns {kernel name: (launches, total us)} of the step."""
     from torch.profiler import ProfilerActivity, profile
 
     from ..config import ApertusConfig
     from ..engine import Engine
     s = dict(APERTUS_8B_LAYER, **(shape or {}))
-    cfg = ApertusConfig.from_dict({
+    cfg = config or ApertusConfig.from_dict({
         "architectures": ["ApertusForCausalLM"], "num_hidden_layers": layers, "hidden_size": s["hidden"],
         "num_attention_heads": s["heads"], "num_key_value_heads": s["kv_heads"], "head_dim": s["head_dim"],
         "intermediate_size": s["intermediate"], "vocab_size": s["vocab"], "rope_theta": 12e6, "rms_norm_eps": 1e-5,
         "max_position_embeddings": 4096, "qk_norm": True, "hidden_act": "xielu"})
+    if config is not None:
+        s["vocab"] = cfg.vocab_size
+        layers = len(cfg.model_spec().order)
     eng = Engine.random(cfg, seed=0, dtype="bfloat16", max_context=4096, max_seqs=max(batch, 1),
                         max_tokens=max(batch * 1280, prefill_tokens + 64), max_step_tokens=max(prefill_tokens, 2048))
     if prefill_tokens:
@@ -274,7 +280,7 @@ def timeline(batch, layers, cached=1023, prefill_tokens=0, shape=None):
     print(f"{layers} layers: {len(last)} kernels in one {what}, "
           f"{last[-1].time_range.end - t0:.1f} us from first start to last end")
     prev = None
-    first_layer_end = 2 + 2 * 9
+    first_layer_end = first or 2 + 2 * 9
     def short(name):
         return name.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0].strip()
     for e in last[:first_layer_end]:
@@ -289,6 +295,7 @@ def timeline(batch, layers, cached=1023, prefill_tokens=0, shape=None):
         count[key] += 1
     for key, v in total.most_common():
         print(f"  {key:32s} n={count[key]:4d}  total {v:8.1f} us  mean {v / count[key]:6.1f} us")
+    return {key: (count[key], v) for key, v in total.items()}
 
 
 def main(argv=None):

@@ -295,24 +295,35 @@ def gated_unit_limit(y, gu, limit, slope, shift):
           "gated_unit_limit")
 
 
-def router_topk(h, wr, top, ids, scores):
-    """ids, scores [n, top]: the ``top`` experts of every row with the largest sigmoid(wr h), logits in 32-bit."""
+def router_topk(h, wr, top, ids, scores, logits=None):
+    """ids, scores [n, top]: the ``top`` experts of every row with the largest sigmoid(wr h), logits in 32-bit. ``logits``
+    [n, experts] float32: the sums wr h if a product kernel has already left them (h is then not read)."""
     _need(h, "h"); _need(wr, "wr", h.dtype); _need(ids, "ids", torch.int32); _need(scores, "scores", torch.float32)
     n, width = h.shape
-    check(lib().ti_router_topk(h.data_ptr(), wr.data_ptr(), n, width, wr.shape[0], top, ids.data_ptr(), scores.data_ptr(),
+    if logits is not None:
+        _need(logits, "logits", torch.float32)
+        if tuple(logits.shape) != (n, wr.shape[0]):
+            raise KernelError(f"router_topk: logits {tuple(logits.shape)} for {n} rows and {wr.shape[0]} experts")
+    check(lib().ti_router_topk(h.data_ptr(), wr.data_ptr(), _ptr(logits), n, width, wr.shape[0], top, ids.data_ptr(), scores.data_ptr(),
                                dtype_code(h.dtype), _stream()), "router_topk")
 
 
-def expert_plan_sizes(pairs: int, experts: int):
-    """(words of the plan, most row tiles) for ``pairs`` (token, choice) pairs over ``experts`` experts."""
-    return int(lib().ti_expert_plan_words(pairs, experts)), int(lib().ti_expert_plan_max_tiles(pairs, experts))
+EXPERT_TILE_ROWS = 32          # the smallest tile of rows the grouped products take (csrc/tile_gemm.cuh)
 
 
-def expert_plan(ids, experts, pair_row, row_pair, plan):
+def expert_plan_sizes(pairs: int, experts: int, tile: int):
+    """(most tiles, rows of the padded layout) for ``pairs`` (token, choice) pairs over ``experts`` experts in tiles of
+    ``tile`` rows."""
+    tiles = int(lib().ti_expert_plan_max_tiles(pairs, experts, tile))
+    return tiles, tiles * tile
+
+
+def expert_plan(ids, experts, tile, pair_row, row_pair, plan):
+    """``row_pair`` [capacity] and ``plan`` [1 + capacity / tile] are filled for the pairs ``ids`` [n, top]."""
     _need(ids, "ids", torch.int32); _need(pair_row, "pair_row", torch.int32); _need(row_pair, "row_pair", torch.int32)
     _need(plan, "plan", torch.int32)
-    check(lib().ti_expert_plan(ids.data_ptr(), ids.numel(), experts, pair_row.data_ptr(), row_pair.data_ptr(), plan.data_ptr(), _stream()),
-          "expert_plan")
+    check(lib().ti_expert_plan(ids.data_ptr(), ids.numel(), experts, tile, row_pair.numel(), pair_row.data_ptr(), row_pair.data_ptr(),
+                               plan.data_ptr(), _stream()), "expert_plan")
 
 
 def expert_gather(xs, h, row_pair, scores, top, scale_input=True):
@@ -321,15 +332,15 @@ def expert_gather(xs, h, row_pair, scores, top, scale_input=True):
                                  int(bool(scale_input)), dtype_code(xs.dtype), _stream()), "expert_gather")
 
 
-def grouped_gemm(y, x, w, plan, max_tiles, gated=False, limit=0.0, slope=0.0, shift=0.0):
-    """Rows of x grouped by expert (``plan``): y[row] = w[expert] x[row]; ``gated``: w [experts, 2 * out, in] holds gate
-    rows then up rows and y is the clamped gated unit's activation."""
+def grouped_gemm(y, x, w, plan, tile, gated=False, limit=0.0, slope=0.0, shift=0.0):
+    """Rows of x grouped by expert in tiles of ``tile`` rows (``plan``): y[row] = w[expert] x[row], on the CUDA cores;
+    ``gated``: w [experts, 2 * out, in] holds gate rows then up rows and y is the clamped gated unit's activation."""
     _need(y, "y"); _need(x, "x", y.dtype); _need(w, "w", y.dtype); _need(plan, "plan", torch.int32)
     experts, rows_w, k = w.shape
     out = rows_w // 2 if gated else rows_w
     if x.shape[1] != k or y.shape[1] != out or x.shape[0] != y.shape[0]:
         raise KernelError(f"grouped_gemm: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)} do not fit")
-    check(lib().ti_grouped_gemm(y.data_ptr(), x.data_ptr(), w.data_ptr(), plan.data_ptr(), max_tiles, experts, out, k, int(bool(gated)),
+    check(lib().ti_grouped_gemm(y.data_ptr(), x.data_ptr(), w.data_ptr(), plan.data_ptr(), x.shape[0], tile, out, k, int(bool(gated)),
                                 limit, slope, shift, dtype_code(y.dtype), _stream()), "grouped_gemm")
 
 

@@ -83,17 +83,21 @@ class LatentAttention(Mixer):
         ops.latent_inputs(rows, cq, cache.k, self.w_q_norm, self.w_kv_norm, self.eps, meta.slot_mapping, Q, R)
         q = rt.buffer("latent.q", (n, H, D))
         self.uq.forward(cq, q.view(n, H * D))
-        q_lat = rt.buffer("latent.q_latent", (n, H, R))
-        ops.head_gemm(q_lat, q, self.uk_t)
-        attn = rt.buffer("latent.attended", (n, H, R))
-        done = False
+        fast = None
         if rt.fast:
             from ..kernels import fast
+        q_lat = rt.buffer("latent.q_latent", (n, H, R))
+        if not (fast is not None and fast.head_linear(q_lat, q, self.uk_t)):
+            ops.head_gemm(q_lat, q, self.uk_t)
+        attn = rt.buffer("latent.attended", (n, H, R))
+        done = False
+        if fast is not None:
             done = fast.attention(attn.view(n, H * R), q_lat, cache, meta, step, self.attn_spec)
         if not done:
             ops.attention_plain(attn.view(n, H * R), q_lat, cache.k, cache.v, meta.block_table, step.tok_slot, step.positions,
                                 s.scale, H, 1, R, cache.page_size, window=s.window or 0)
         values = rt.buffer("latent.values", (n, H, V))
-        ops.head_gemm(values, attn, self.uv)
+        if not (fast is not None and fast.head_linear(values, attn, self.uv)):
+            ops.head_gemm(values, attn, self.uv)
         proj = rt.buffer("mixer.delta", (n, s.hidden_size))
         return self.o.forward(values.view(n, H * V), proj, allow_partials=True)

@@ -37,6 +37,7 @@ class RoutedExperts(FeedForward):
             raise ValueError("routed_experts: only unnormalised sigmoid scores are built")
         get = lambda name: rt.param(tensors[p + name])
         self.router = get(n["router"])
+        self.router_linear = Linear(self.router, rt, "router")
         units = [p + n["expert"].format(e) for e in range(self.experts)]
         unit = lambda u, k: rt.param(tensors[u + n[k]])
         # Every expert's gate rows then its up rows, expert after expert; the down matrices likewise.
@@ -70,14 +71,21 @@ class RoutedExperts(FeedForward):
         n, W = h.shape
         F, top, E = spec.intermediate_size, self.top, self.experts
         pairs = n * top
+        fast = None
+        if rt.fast:
+            from ..kernels import fast
         ids = rt.buffer("experts.ids", (n, top), torch.int32)
         scores = rt.buffer("experts.scores", (n, top), torch.float32)
-        ops.router_topk(h, self.router, top, ids, scores)
-        words, max_tiles = ops.expert_plan_sizes(pairs, E)
+        logits = None
+        if fast is not None:                     # the router's 32-bit sums from a product kernel, where one takes the sizes
+            logits = fast.linear_f32(self.router_linear, h, rt.buffer("experts.logits", (n, E), torch.float32))
+        ops.router_topk(h, self.router, top, ids, scores, logits)
+        tile = fast.grouped_tile(pairs, E) if fast is not None else ops.EXPERT_TILE_ROWS
+        max_tiles, rows = ops.expert_plan_sizes(pairs, E, tile)
         pair_row = rt.buffer("experts.pair_row", (pairs,), torch.int32)
-        row_pair = rt.buffer("experts.row_pair", (pairs,), torch.int32)
-        plan = rt.buffer("experts.plan", (words,), torch.int32)
-        ops.expert_plan(ids, E, pair_row, row_pair, plan)
+        row_pair = rt.buffer("experts.row_pair", (rows,), torch.int32)
+        plan = rt.buffer("experts.plan", (1 + max_tiles,), torch.int32)
+        ops.expert_plan(ids, E, tile, pair_row, row_pair, plan)
         shared = None
         if self.shared_size:
             gu = rt.buffer("experts.shared_gate_up", (n, 2 * self.shared_size))
@@ -86,12 +94,17 @@ class RoutedExperts(FeedForward):
             ops.gated_unit_limit(act, gu, self.shared_limit, self.slope, self.shift)
             shared = rt.buffer("experts.shared_out", (n, W))
             self.shared_down.forward(act, shared)
-        xs = rt.buffer("experts.rows", (pairs, W))
+        xs = rt.buffer("experts.rows", (rows, W))
         ops.expert_gather(xs, h, row_pair, scores, top, self.scale_input)
-        act = rt.buffer("experts.act", (pairs, F))
-        ops.grouped_gemm(act, xs, self.gate_up, plan, max_tiles, gated=True, limit=self.limit, slope=self.slope, shift=self.shift)
-        ys = rt.buffer("experts.out_rows", (pairs, W))
-        ops.grouped_gemm(ys, act, self.down, plan, max_tiles)
+        act = rt.buffer("experts.act", (rows, F))
+        gu = rt.buffer("experts.gate_up", (rows, 2 * F))
+        if fast is not None and fast.grouped_linear(gu, xs, self.gate_up, plan, tile):
+            ops.gated_unit_limit(act, gu, self.limit, self.slope, self.shift)
+        else:
+            ops.grouped_gemm(act, xs, self.gate_up, plan, tile, gated=True, limit=self.limit, slope=self.slope, shift=self.shift)
+        ys = rt.buffer("experts.out_rows", (rows, W))
+        if not (fast is not None and fast.grouped_linear(ys, act, self.down, plan, tile)):
+            ops.grouped_gemm(ys, act, self.down, plan, tile)
         out = rt.buffer("feed_forward.delta", (n, W))
         ops.expert_combine(out, ys, pair_row, scores, shared, top, scale_output=not self.scale_input)
         return out
