@@ -63,27 +63,66 @@ extern "C" int ti_gated_token_embedding(void* g, const void* table, const int* i
     return ti_check_launch("gated_token_embedding");
 }
 
+// Rows in tiles that belong to units with limits of their own: `plan` [0] = tiles in use, [1 + t] = the unit of tile t
+// (rows of tiles beyond those in use are left alone), `limits` [units]. Without a plan every row uses `limit`.
+// A thread handles one 16-byte vector of outputs.
 template <typename T>
-__global__ void gated_unit_limit_kernel(T* __restrict__ y, const T* gu, int ff, size_t count, float limit, float slope, float shift) {
-    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
+__global__ void gated_unit_limit_kernel(T* __restrict__ y, const T* gu, int n, int ff, float limit, const int* plan, int tile,
+                                        const float* __restrict__ limits, float slope, float shift) {
+    constexpr int N = Vec16<T>::N;
+    const int vecs = ff / N;
     pdl_enter();
-    for (; i < count; i += stride) {
-        const size_t t = i / ff, j = i % ff;
-        const float a = fminf(to_f32(__ldcg(gu + t * 2 * ff + j)), limit);
-        const float b = fminf(fmaxf(to_f32(__ldcg(gu + t * 2 * ff + ff + j)), -limit), limit);
-        y[i] = from_f32<T>(a / (1.0f + expf(-slope * a)) * (b + shift));
+    const int tiles = plan != nullptr ? __ldcg(plan) : 0;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (long long)n * vecs; i += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(i / vecs), j = (int)(i % vecs) * N;
+        float lim = limit;
+        if (plan != nullptr) {
+            if (t / tile >= tiles) continue;
+            lim = limits[__ldcg(plan + 1 + t / tile)];
+        }
+        Vec16<T> a, b;
+        a.load_cg(gu + (size_t)t * 2 * ff + j);
+        b.load_cg(gu + (size_t)t * 2 * ff + ff + j);
+#pragma unroll
+        for (int e = 0; e < N; ++e) {
+            const float g = fminf(a.v[e], lim), u = fminf(fmaxf(b.v[e], -lim), lim);
+            a.v[e] = g / (1.0f + __expf(-slope * g)) * (u + shift);
+        }
+        a.store(y + (size_t)t * ff + j);
     }
 }
 
-extern "C" int ti_gated_unit_limit(void* y, const void* gu, int n, int ff, float limit, float slope, float shift, int dtype,
-                                   cudaStream_t stream) {
+template <typename T>
+__global__ void gated_unit_limit_scalar_kernel(T* __restrict__ y, const T* gu, int n, int ff, float limit, const int* plan, int tile,
+                                               const float* __restrict__ limits, float slope, float shift) {
+    pdl_enter();
+    const int tiles = plan != nullptr ? __ldcg(plan) : 0;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (long long)n * ff; i += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(i / ff), j = (int)(i % ff);
+        float lim = limit;
+        if (plan != nullptr) {
+            if (t / tile >= tiles) continue;
+            lim = limits[__ldcg(plan + 1 + t / tile)];
+        }
+        const float g = fminf(to_f32(__ldcg(gu + (size_t)t * 2 * ff + j)), lim);
+        const float u = fminf(fmaxf(to_f32(__ldcg(gu + (size_t)t * 2 * ff + ff + j)), -lim), lim);
+        y[i] = from_f32<T>(g / (1.0f + expf(-slope * g)) * (u + shift));
+    }
+}
+
+extern "C" int ti_gated_unit_limit(void* y, const void* gu, int n, int ff, float limit, const int* plan, int tile, const float* limits,
+                                   float slope, float shift, int dtype, cudaStream_t stream) {
     if (n == 0) return 0;
     TI_REQUIRE(ff > 0, "gated_unit_limit: size %d", ff);
-    const long long count = (long long)n * ff;
-    long long blocks = (count + 255) / 256;
-    if (blocks > ti_sm_count() * 16) blocks = ti_sm_count() * 16;
-    TI_DISPATCH_DTYPE(dtype, (ti_launch(gated_unit_limit_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (T*)y, (const T*)gu, ff,
-                                        (size_t)count, limit, slope, shift)));
+    TI_REQUIRE(plan == nullptr || (tile > 0 && limits != nullptr), "gated_unit_limit: a plan needs its tile size and limits");
+    TI_DISPATCH_DTYPE(dtype, {
+        constexpr int N = Vec16<T>::N;
+        const bool vec = ff % N == 0 && aligned16(y) && aligned16(gu) && sizeof(T) == 2;      // the 32-bit path keeps expf
+        const long long count = vec ? (long long)n * (ff / N) : (long long)n * ff;
+        long long blocks = (count + 255) / 256;
+        if (blocks > ti_sm_count() * 16) blocks = ti_sm_count() * 16;
+        if (vec) ti_launch(gated_unit_limit_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (T*)y, (const T*)gu, n, ff, limit, plan, tile, limits, slope, shift);
+        else ti_launch(gated_unit_limit_scalar_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (T*)y, (const T*)gu, n, ff, limit, plan, tile, limits, slope, shift);
+    });
     return ti_check_launch("gated_unit_limit");
 }

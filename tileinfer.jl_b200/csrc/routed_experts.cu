@@ -23,7 +23,7 @@
 
 template <typename T>
 __global__ void router_topk_kernel(const T* h, const T* __restrict__ wr, const float* logits, int width, int experts, int top,
-                                   int* __restrict__ ids, float* __restrict__ scores) {
+                                   int always, int* __restrict__ ids, float* __restrict__ scores) {
     __shared__ float z[RT_MAX_EXPERTS];
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     pdl_enter();
@@ -54,22 +54,29 @@ __global__ void router_topk_kernel(const T* h, const T* __restrict__ wr, const f
             }
             if (arg >= experts) arg = j;                            // only if every logit left is NaN
             if (lane == 0) {
-                ids[(size_t)t * top + j] = arg;
-                scores[(size_t)t * top + j] = 1.0f / (1.0f + expf(-best));
+                ids[(size_t)t * (top + always) + j] = arg;
+                scores[(size_t)t * (top + always) + j] = 1.0f / (1.0f + expf(-best));
                 z[arg] = -INFINITY;
             }
             __syncwarp();
+        }
+        // Units that every token goes through follow the chosen ones, numbered after the routed experts, with score one.
+        for (int a = lane; a < always; a += 32) {
+            ids[(size_t)t * (top + always) + top + a] = experts + a;
+            scores[(size_t)t * (top + always) + top + a] = 1.0f;
         }
     }
 }
 
 // `logits` [n, experts]: the router's 32-bit sums if a product kernel has computed them (h and wr are then not read), else null.
-extern "C" int ti_router_topk(const void* h, const void* wr, const float* logits, int n, int width, int experts, int top, int* ids,
-                              float* scores, int dtype, cudaStream_t stream) {
+// `always`: units after the routed experts that every token takes besides (ids experts .. experts + always - 1, score 1);
+// ids and scores are [n, top + always].
+extern "C" int ti_router_topk(const void* h, const void* wr, const float* logits, int n, int width, int experts, int top, int always,
+                              int* ids, float* scores, int dtype, cudaStream_t stream) {
     if (n == 0) return 0;
-    TI_REQUIRE(experts >= 1 && experts <= RT_MAX_EXPERTS && top >= 1 && top <= experts, "router_topk: top %d of %d experts", top, experts);
+    TI_REQUIRE(experts >= 1 && experts <= RT_MAX_EXPERTS && top >= 1 && top <= experts && always >= 0, "router_topk: top %d of %d experts", top, experts);
     TI_DISPATCH_DTYPE(dtype, (ti_launch(router_topk_kernel<T>, dim3(n), dim3(RT_THREADS), 0, stream, (const T*)h, (const T*)wr, logits, width,
-                                        experts, top, ids, scores)));
+                                        experts, top, always, ids, scores)));
     return ti_check_launch("router_topk");
 }
 
@@ -150,12 +157,14 @@ extern "C" int ti_expert_gather(void* xs, const void* h, const int* row_pair, co
 // matrix of the plan's tile that holds those rows.
 template <typename T, bool GATED>
 __global__ void __launch_bounds__(TG_THREADS) grouped_gemm_kernel(T* __restrict__ y, const T* x, const T* __restrict__ w, const int* plan,
-                                                                  int tile, int out, int in, float limit, float slope, float shift) {
+                                                                  int tile, int out, int in, const float* __restrict__ limits, float slope,
+                                                                  float shift) {
     __shared__ TileGemmSmem s;
     pdl_enter();
     const int row0 = blockIdx.x * TG_ROWS, t = row0 / tile;
     if (t >= __ldcg(plan)) return;
     const int e = __ldcg(plan + 1 + t), rows = TG_ROWS;
+    const float limit = GATED ? limits[e] : 0.f;
     const int col0 = blockIdx.y * TG_COLS, cols = min(TG_COLS, out - col0);
     const T* xb = x + (size_t)row0 * in;
     auto xrow = [&](int r) { return xb + (size_t)r * in; };
@@ -182,14 +191,16 @@ __global__ void __launch_bounds__(TG_THREADS) grouped_gemm_kernel(T* __restrict_
     }
 }
 
+// `limits` [matrices]: every unit's clamp (gated only).
 extern "C" int ti_grouped_gemm(void* y, const void* x, const void* w, const int* plan, int rows, int tile, int out, int in,
-                               int gated, float limit, float slope, float shift, int dtype, cudaStream_t stream) {
+                               int gated, const float* limits, float slope, float shift, int dtype, cudaStream_t stream) {
     if (rows == 0) return 0;
+    TI_REQUIRE(!gated || limits != nullptr, "grouped_gemm: a gated unit needs its limits");
     TI_REQUIRE(out > 0 && in > 0 && tile % TG_ROWS == 0 && rows % tile == 0, "grouped_gemm: bad sizes out=%d in=%d rows=%d tile=%d", out, in, rows, tile);
     const dim3 grid(rows / TG_ROWS, (out + TG_COLS - 1) / TG_COLS);
     TI_DISPATCH_DTYPE(dtype, {
-        if (gated) ti_launch(grouped_gemm_kernel<T, true>, grid, dim3(TG_THREADS), 0, stream, (T*)y, (const T*)x, (const T*)w, plan, tile, out, in, limit, slope, shift);
-        else ti_launch(grouped_gemm_kernel<T, false>, grid, dim3(TG_THREADS), 0, stream, (T*)y, (const T*)x, (const T*)w, plan, tile, out, in, limit, slope, shift);
+        if (gated) ti_launch(grouped_gemm_kernel<T, true>, grid, dim3(TG_THREADS), 0, stream, (T*)y, (const T*)x, (const T*)w, plan, tile, out, in, limits, slope, shift);
+        else ti_launch(grouped_gemm_kernel<T, false>, grid, dim3(TG_THREADS), 0, stream, (T*)y, (const T*)x, (const T*)w, plan, tile, out, in, limits, slope, shift);
     });
     return ti_check_launch("grouped_gemm");
 }

@@ -94,9 +94,11 @@ extern "C" int ti_norm32(void* y, const void* x, int x_is_f32, const void* w, in
     return ti_check_launch("norm32");
 }
 
+// `gather` [n, per_row]: the branch's row is the sum, in that order and in 32-bit, of the rows gather[row][0 .. per_row) of
+// `delta` (the outputs of the units a token went through), instead of row `row` of `delta`.
 template <typename T>
 __global__ void branch_norm_add32_kernel(float* x, const T* delta, const float* partials, int n_partials, size_t partial_stride,
-                                         const T* __restrict__ w, int offset, float eps, float mult, T* __restrict__ h,
+                                         const int* gather, int per_row, const T* __restrict__ w, int offset, float eps, float mult, T* __restrict__ h,
                                          const T* __restrict__ w_out, int offset_out, float eps_out, int size) {
     extern __shared__ float row_d[];           // [size]: the branch's row, then the stream's new row
     __shared__ float scratch[33];
@@ -109,6 +111,10 @@ __global__ void branch_norm_add32_kernel(float* x, const T* delta, const float* 
             const float* p = partials + (size_t)blockIdx.x * size + i;
             d = __ldcg(p);
             for (int s = 1; s < n_partials; ++s) d += __ldcg(p + (size_t)s * partial_stride);
+        } else if (gather != nullptr) {
+            d = 0.f;
+            for (int j = 0; j < per_row; ++j)
+                d += to_f32(__ldcg(delta + (size_t)__ldcg(gather + (size_t)blockIdx.x * per_row + j) * size + i));
         } else {
             d = to_f32(__ldcg(delta + (size_t)blockIdx.x * size + i));
         }
@@ -140,12 +146,13 @@ __global__ void branch_norm_add32_kernel(float* x, const T* delta, const float* 
 }
 
 extern "C" int ti_branch_norm_add32(float* x, const void* delta, const float* partials, int n_partials, long long partial_stride,
-                                    const void* w, int offset, float eps, float mult, void* h, const void* w_out, int offset_out,
+                                    const int* gather, int per_row, const void* w, int offset, float eps, float mult, void* h, const void* w_out, int offset_out,
                                     float eps_out, int n_rows, int size, int dtype, cudaStream_t stream) {
     if (n_rows == 0) return 0;
     TI_REQUIRE(size > 0 && size <= 50000, "branch_norm_add32: size %d", size);
     TI_REQUIRE((delta != nullptr) != (partials != nullptr), "branch_norm_add32: give delta or partials, not both");
     TI_REQUIRE(partials == nullptr || n_partials >= 1, "branch_norm_add32: n_partials %d", n_partials);
+    TI_REQUIRE(gather == nullptr || (delta != nullptr && per_row >= 1), "branch_norm_add32: gathered rows need delta and a count");
     const int threads = row_threads(size);
     const size_t smem = (size_t)size * sizeof(float);
     TI_DISPATCH_DTYPE(dtype, {
@@ -157,7 +164,7 @@ extern "C" int ti_branch_norm_add32(float* x, const void* delta, const float* pa
             }
         }
         ti_launch(branch_norm_add32_kernel<T>, dim3(n_rows), dim3(threads), smem, stream, x, (const T*)delta, partials, n_partials,
-                  (size_t)partial_stride, (const T*)w, offset, eps, mult, (T*)h, (const T*)w_out, offset_out, eps_out, size);
+                  (size_t)partial_stride, gather, per_row, (const T*)w, offset, eps, mult, (T*)h, (const T*)w_out, offset_out, eps_out, size);
     });
     return ti_check_launch("branch_norm_add32");
 }

@@ -162,16 +162,16 @@ _SIGNATURES.update({
     "ti_embed_positions32": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "ti_cast_rows": [_P, _P, _L, _I, _P],
     "ti_norm32": [_P, _P, _I, _P, _I, _I, _F, _I, _I, _P],
-    "ti_branch_norm_add32": [_P, _P, _P, _I, _L, _P, _I, _F, _F, _P, _P, _I, _F, _I, _I, _I, _P],
+    "ti_branch_norm_add32": [_P, _P, _P, _I, _L, _P, _I, _P, _I, _F, _F, _P, _P, _I, _F, _I, _I, _I, _P],
     "ti_latent_inputs": [_P, _L, _P, _I, _L, _P, _P, _P, _P, _F, _P, _I, _I, _I, _I, _P],
     "ti_head_gemm": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _I, _P],
     "ti_gelu": [_P, _P, _L, _I, _I, _P],
     "ti_gated_token_embedding": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-    "ti_gated_unit_limit": [_P, _P, _I, _I, _F, _F, _F, _I, _P],
-    "ti_router_topk": [_P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P],
+    "ti_gated_unit_limit": [_P, _P, _I, _I, _F, _P, _I, _P, _F, _F, _I, _P],
+    "ti_router_topk": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _I, _P],
     "ti_expert_plan": [_P, _I, _I, _I, _I, _P, _P, _P, _P],
     "ti_expert_gather": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
-    "ti_grouped_gemm": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _F, _I, _P],
+    "ti_grouped_gemm": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _F, _F, _I, _P],
     "ti_gemm_tcgen05_grouped": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "ti_gemm_tcgen05_heads": [_P, _P, _P, _I, _I, _I, _I, _P, _P],
     "ti_expert_combine": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],

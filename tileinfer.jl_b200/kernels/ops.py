@@ -223,12 +223,20 @@ def norm32(y, x, w, eps, offset=False):
                           int(bool(offset)), dtype_code(y.dtype), _stream()), "norm32")
 
 
-def branch_norm_add32(x, delta, w, eps, mult, offset=False, h=None, out_norm=None):
+def branch_norm_add32(x, delta, w, eps, mult, offset=False, h=None, out_norm=None, gather=None):
     """x += mult * delta / rms(delta) * g(w) in 32-bit (``delta``: [n, size] of w's type, or 32-bit partial sums
-    [s, n, size]); then, with ``h``, h = x rounded, or h = x / rms(x) * g(w_out) for ``out_norm`` = (w_out, eps, offset)."""
+    [s, n, size]); then, with ``h``, h = x rounded, or h = x / rms(x) * g(w_out) for ``out_norm`` = (w_out, eps, offset).
+    ``gather`` [n, k] int32: row t of the branch is the sum of the rows gather[t, :] of ``delta`` [rows, size]."""
     _need(x, "x", torch.float32); _need(w, "w")
     n, size = x.shape
-    if delta.dim() == 3:
+    g_args = (None, 0)
+    if gather is not None:
+        _need(gather, "gather", torch.int32); _need(delta, "delta", w.dtype)
+        if gather.shape[0] != n or delta.shape[1] != size:
+            raise KernelError(f"branch_norm_add32: gather {tuple(gather.shape)}, rows {tuple(delta.shape)} for a stream of {tuple(x.shape)}")
+        d_args = (delta.data_ptr(), None, 0, 0)
+        g_args = (gather.data_ptr(), gather.shape[1])
+    elif delta.dim() == 3:
         _need(delta, "partial sums", torch.float32)
         d_args = (None, delta.data_ptr(), delta.shape[0], delta.stride(0))
     else:
@@ -239,7 +247,7 @@ def branch_norm_add32(x, delta, w, eps, mult, offset=False, h=None, out_norm=Non
     w_out, eps_out, offset_out = out_norm if out_norm is not None else (None, 0.0, False)
     if w_out is not None:
         _need(w_out, "w_out", w.dtype)
-    check(lib().ti_branch_norm_add32(x.data_ptr(), *d_args, w.data_ptr(), int(bool(offset)), eps, mult, _ptr(h), _ptr(w_out),
+    check(lib().ti_branch_norm_add32(x.data_ptr(), *d_args, *g_args, w.data_ptr(), int(bool(offset)), eps, mult, _ptr(h), _ptr(w_out),
                                      int(bool(offset_out)), eps_out, n, size, dtype_code(w.dtype), _stream()), "branch_norm_add32")
 
 
@@ -285,26 +293,32 @@ def gated_token_embedding(g, table, ids, first):
                                          dtype_code(g.dtype), _stream()), "gated_token_embedding")
 
 
-def gated_unit_limit(y, gu, limit, slope, shift):
-    """y[t, j] = a * sigmoid(slope * a) * (b + shift), a = min(gu[t, j], limit), b = clamp(gu[t, ff + j], -limit, limit)."""
+def gated_unit_limit(y, gu, limit, slope, shift, plan=None, tile=0, limits=None):
+    """y[t, j] = a * sigmoid(slope * a) * (b + shift), a = min(gu[t, j], limit), b = clamp(gu[t, ff + j], -limit, limit).
+    With ``plan`` (rows in tiles of ``tile`` rows, each tile one unit's) the limit of a row is ``limits[unit]``."""
     _need(y, "y"); _need(gu, "gu", y.dtype)
     n, ff = y.shape
     if tuple(gu.shape) != (n, 2 * ff):
         raise KernelError(f"gated_unit_limit: gu {tuple(gu.shape)} for y {tuple(y.shape)}")
-    check(lib().ti_gated_unit_limit(y.data_ptr(), gu.data_ptr(), n, ff, limit, slope, shift, dtype_code(y.dtype), _stream()),
-          "gated_unit_limit")
+    if plan is not None:
+        _need(plan, "plan", torch.int32); _need(limits, "limits", torch.float32)
+    check(lib().ti_gated_unit_limit(y.data_ptr(), gu.data_ptr(), n, ff, limit, _ptr(plan), tile, _ptr(limits), slope, shift,
+                                    dtype_code(y.dtype), _stream()), "gated_unit_limit")
 
 
-def router_topk(h, wr, top, ids, scores, logits=None):
-    """ids, scores [n, top]: the ``top`` experts of every row with the largest sigmoid(wr h), logits in 32-bit. ``logits``
-    [n, experts] float32: the sums wr h if a product kernel has already left them (h is then not read)."""
+def router_topk(h, wr, top, ids, scores, logits=None, always=0):
+    """ids, scores [n, top + always]: the ``top`` experts of every row with the largest sigmoid(wr h), logits in 32-bit,
+    followed by ``always`` units that every row takes (numbered after the experts, score 1). ``logits`` [n, experts]
+    float32: the sums wr h if a product kernel has already left them (h is then not read)."""
+    if tuple(ids.shape) != (h.shape[0], top + always) or ids.shape != scores.shape:
+        raise KernelError(f"router_topk: ids {tuple(ids.shape)}, scores {tuple(scores.shape)} for top {top} + {always}")
     _need(h, "h"); _need(wr, "wr", h.dtype); _need(ids, "ids", torch.int32); _need(scores, "scores", torch.float32)
     n, width = h.shape
     if logits is not None:
         _need(logits, "logits", torch.float32)
         if tuple(logits.shape) != (n, wr.shape[0]):
             raise KernelError(f"router_topk: logits {tuple(logits.shape)} for {n} rows and {wr.shape[0]} experts")
-    check(lib().ti_router_topk(h.data_ptr(), wr.data_ptr(), _ptr(logits), n, width, wr.shape[0], top, ids.data_ptr(), scores.data_ptr(),
+    check(lib().ti_router_topk(h.data_ptr(), wr.data_ptr(), _ptr(logits), n, width, wr.shape[0], top, always, ids.data_ptr(), scores.data_ptr(),
                                dtype_code(h.dtype), _stream()), "router_topk")
 
 
@@ -332,16 +346,19 @@ def expert_gather(xs, h, row_pair, scores, top, scale_input=True):
                                  int(bool(scale_input)), dtype_code(xs.dtype), _stream()), "expert_gather")
 
 
-def grouped_gemm(y, x, w, plan, tile, gated=False, limit=0.0, slope=0.0, shift=0.0):
+def grouped_gemm(y, x, w, plan, tile, gated=False, limits=None, slope=0.0, shift=0.0):
     """Rows of x grouped by expert in tiles of ``tile`` rows (``plan``): y[row] = w[expert] x[row], on the CUDA cores;
-    ``gated``: w [experts, 2 * out, in] holds gate rows then up rows and y is the clamped gated unit's activation."""
+    ``gated``: w [experts, 2 * out, in] holds gate rows then up rows and y is the clamped gated unit's activation, each
+    unit with its own ``limits[unit]``."""
+    if gated:
+        _need(limits, "limits", torch.float32)
     _need(y, "y"); _need(x, "x", y.dtype); _need(w, "w", y.dtype); _need(plan, "plan", torch.int32)
     experts, rows_w, k = w.shape
     out = rows_w // 2 if gated else rows_w
     if x.shape[1] != k or y.shape[1] != out or x.shape[0] != y.shape[0]:
         raise KernelError(f"grouped_gemm: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)} do not fit")
     check(lib().ti_grouped_gemm(y.data_ptr(), x.data_ptr(), w.data_ptr(), plan.data_ptr(), x.shape[0], tile, out, k, int(bool(gated)),
-                                limit, slope, shift, dtype_code(y.dtype), _stream()), "grouped_gemm")
+                                _ptr(limits), slope, shift, dtype_code(y.dtype), _stream()), "grouped_gemm")
 
 
 def expert_combine(out, y, pair_row, scores, shared, top, scale_output=False):

@@ -63,8 +63,19 @@ class RMSNorm32(Norm):
 
     def branch_add(self, x, delta, mult, h=None, next_norm=None):
         out_norm = next_norm.out_args() if next_norm is not None else None
-        ops.branch_norm_add32(x, delta, self.weight, self.eps, mult, self.offset, h, out_norm)
+        if isinstance(delta, GatheredRows):
+            ops.branch_norm_add32(x, delta.rows, self.weight, self.eps, mult, self.offset, h, out_norm, gather=delta.index)
+        else:
+            ops.branch_norm_add32(x, delta, self.weight, self.eps, mult, self.offset, h, out_norm)
         return h
+
+
+class GatheredRows:
+    """A sublayer's output that is still in pieces: row t is the sum of the rows ``index[t, :]`` of ``rows`` (the units a
+    token went through). A norm that offers ``branch_add`` adds them up while it reads them."""
+
+    def __init__(self, rows, index):
+        self.rows, self.index = rows, index
 
 
 class StreamCast(Norm):
