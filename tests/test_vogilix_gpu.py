@@ -229,3 +229,150 @@ def test_trace_replay(models, dtype):
     assert len(by_request) == 5 + 5 + 3 + 3
     for rid, g in by_request.items():
         vc.compare(m, reqs[rid[1:]], g, DTYPES[dtype], f"replay {dtype} {rid}")
+
+
+def test_bfloat16_steps_take_the_tensor_core_kernels(models):
+    """Case B's sizes are ones the fast kernels take: a prompt and a decode step in bfloat16 go through the grouped and the
+    per-head tensor-core products and the paged attention kernels, not through their plain stand-ins."""
+    from tileinfer_b200.kernels import library
+    m = models["B"]
+    engine = m.engine("bfloat16", graphs=False)
+    slot = engine.new_sequence()
+    library.call_counts.clear()
+    engine.step([(slot, vc.prompts(m.vocab, [450], 61)[0])])
+    engine.step([(slot, [5])])
+    engine.free_sequence(slot)
+    engine.check_health()
+    used = library.call_counts
+    assert used.get("ti_gemm_tcgen05_grouped", 0) == 4 and used.get("ti_gemm_tcgen05_heads", 0) == 8
+    assert used.get("ti_attention_prefill_tc", 0) == 2 and used.get("ti_attention_decode_shared", 0) == 2
+    assert "ti_grouped_gemm" not in used and "ti_head_gemm" not in used and "ti_attention_plain" not in used
+
+
+@pytest.mark.parametrize("dtype", sorted(DTYPES))
+def test_mechanisms_alone(dtype):
+    """The kernels of the design one at a time against the plain implementation's functions, at sizes of their own:
+    the 32-bit stream's update, the norms, the latents, a product per head, the activations, the router, the routed
+    units with and without a shared one."""
+    from tileinfer_b200.kernels import ops
+    T = DTYPES[dtype]
+    g = torch.Generator().manual_seed(7)
+    R = lambda *shape, s=1.0: plain.rnd(torch.randn(*shape, generator=g) * s, T)
+    dev = lambda t: t.to(T).cuda() if t.is_floating_point() else t.cuda()
+    close = lambda got, ref, what: _close(got, ref, T, what)
+    n, size = 9, 88
+    # x += m * d / rms(d) * (1 + w); h = x / rms(x) * w2, or h = x
+    x, d, w, w2 = torch.randn(n, size, generator=g), R(n, size, s=3.0), R(size, s=0.2), R(size) + 1
+    for parts in (None, 3):
+        for out_norm in (None, (dev(w2), 2e-5, False)):
+            xs, h = x.clone().cuda(), torch.empty(n, size, dtype=T, device="cuda")
+            delta = dev(d) if parts is None else torch.stack([d.float() * f for f in (0.5, 0.25, 0.25)]).cuda()
+            ops.branch_norm_add32(xs, delta, dev(w), 1e-5, 0.7, True, h, out_norm)
+            ref = x + 0.7 * plain.norm_offset(d, w, 1e-5)
+            assert xs.dtype == torch.float32 and float((xs.cpu() - ref).abs().max()) < 1e-5
+            close(h, ref if out_norm is None else plain.norm_plain(ref, w2, 2e-5), "stream update")
+    # rows gathered and added up by the update itself
+    rows, index = R(20, size), torch.randint(0, 20, (n, 3), generator=g, dtype=torch.int32)
+    xs = x.clone().cuda()
+    ops.branch_norm_add32(xs, dev(rows), dev(w), 1e-5, 1.0, False, None, None, gather=index.cuda())
+    ref = x + plain.norm_plain(rows[index.long()].sum(1), w, 1e-5)
+    assert float((xs.cpu() - ref).abs().max()) < 1e-5
+    # norms of a 32-bit or a rounded input
+    y = torch.empty(n, size, dtype=T, device="cuda")
+    ops.norm32(y, x.cuda(), dev(w), 1e-6, True)
+    close(y, plain.norm_offset(x, w, 1e-6), "norm of the stream")
+    ops.norm32(y, dev(d), dev(w2), 1e-6, False)
+    close(y, plain.norm_plain(d, w2, 1e-6), "norm of a rounded input")
+    # embedding + learned positions
+    E, P = R(30, size), R(40, size)
+    ids, pos = torch.tensor([3, 29, 0, 7], dtype=torch.int32), torch.tensor([0, 39, 5, 5], dtype=torch.int32)
+    xs, status = torch.empty(4, size, device="cuda"), torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.embed_positions32(xs, dev(E), dev(P), ids.cuda(), pos.cuda(), status)
+    assert torch.equal(xs.cpu(), E[ids.long()] + P[pos.long()]) and int(status.item()) == 0
+    # latents: two norms with plain weights, one to a buffer, one to the pool at scattered places
+    q_rank, kv_rank = 24, 40
+    raw, wq, wkv = R(n, q_rank + kv_rank, s=2.0), R(q_rank) + 1, R(kv_rank) + 1
+    cq, pool = torch.empty(n, q_rank, dtype=T, device="cuda"), torch.zeros(64, kv_rank, dtype=T, device="cuda")
+    places = torch.tensor([5, 63, 0, 17, 18, 40, 2, 9, 33], dtype=torch.int32)
+    ops.latent_inputs(dev(raw), cq, pool, dev(wq), dev(wkv), 1e-6, places.cuda(), q_rank, kv_rank)
+    close(cq, plain.norm_plain(raw[:, :q_rank], wq, 1e-6), "query latent")
+    close(pool[places.long().cuda()], plain.norm_plain(raw[:, q_rank:], wkv, 1e-6), "key/value latent")
+    assert float(pool.float().abs().sum(1)[1]) == 0.0
+    # a product per head
+    heads, out_h, in_h = 3, 40, 24
+    xh, wh = R(n, heads, in_h), R(heads, out_h, in_h, s=0.3)
+    yh = torch.empty(n, heads, out_h, dtype=T, device="cuda")
+    ops.head_gemm(yh, dev(xh), dev(wh))
+    close(yh, torch.einsum("hoi,nhi->nho", wh.double(), xh.double()).float(), "product per head")
+    if T == torch.bfloat16:
+        from tileinfer_b200.kernels import fast
+        xb = R(300, heads, in_h)
+        yb = torch.empty(300, heads, out_h, dtype=T, device="cuda")
+        assert fast.head_linear(yb, dev(xb), dev(wh))
+        fast.check_status()
+        close(yb, torch.einsum("hoi,nhi->nho", wh.double(), xb.double()).float(), "product per head on the tensor cores")
+    # activations
+    z = R(n, size, s=2.0)
+    ops.gelu(y, dev(z), ops.ACT_GELU_ERF)
+    close(y, plain.gelu_erf(z.double()).float(), "gelu")
+    table, tok = R(30, 2 * size), torch.randint(0, 30, (n,), generator=g, dtype=torch.int32)
+    gz = dev(z).clone()
+    ops.gated_token_embedding(gz, dev(table), tok.cuda(), size)
+    close(gz, (plain.gelu_tanh(z.double()) * table[tok.long(), size:].double()).float(), "gated token vector")
+    gu = R(n, 2 * 48, s=2.0)
+    act = torch.empty(n, 48, dtype=T, device="cuda")
+    ops.gated_unit_limit(act, dev(gu), 1.25, 1.702, 1.0)
+    a, b = gu[:, :48].clamp(max=1.25).double(), gu[:, 48:].clamp(-1.25, 1.25).double()
+    close(act, (a * torch.sigmoid(1.702 * a) * (b + 1)).float(), "gated unit")
+    # router: the largest logits, ties to the smaller index, always-on units behind them
+    hr, wr = R(n, size), R(7, size, s=0.3)
+    wr[4] = wr[2]                                                  # two experts with equal logits
+    ids_out = torch.empty(n, 5, dtype=torch.int32, device="cuda")
+    sc_out = torch.empty(n, 5, dtype=torch.float32, device="cuda")
+    ops.router_topk(dev(hr), dev(wr), 3, ids_out, sc_out, always=2)
+    zr = (hr.double() @ wr.double().t())
+    order = sorted(range(7), key=lambda e: (-float(zr[0, e]), e))[:3]
+    assert ids_out[0].tolist() == order + [7, 8] and sc_out[0, 3:].tolist() == [1.0, 1.0]
+    assert torch.allclose(sc_out[:, :3].cpu(), torch.sigmoid(torch.sort(zr, descending=True).values[:, :3]).float(), atol=1e-5)
+    for row in ids_out.cpu().tolist():
+        assert not (4 in row[:3] and 2 not in row[:3])             # of equal logits the smaller index goes first
+
+
+def _close(got, ref, T, what):
+    tol = (1e-5 if T == torch.float32 else 2.0 ** -7) * max(1.0, float(ref.abs().max()))
+    err = float((got.float().cpu() - ref.float()).abs().max())
+    assert err <= tol, f"{what}: |d| = {err:.3g} > {tol:.3g}"
+
+
+@pytest.mark.parametrize("dtype", sorted(DTYPES))
+@pytest.mark.parametrize("shared", [0, 56, 40])
+def test_routed_units_alone(dtype, shared):
+    """The routed feed-forward part alone on random inputs against the plain implementation: without a shared unit, with
+    one that is no multiple of an expert's size, and with one of exactly an expert's size; few rows and many."""
+    from tileinfer_b200.config import FeedForwardSpec
+    from tileinfer_b200.parts import Runtime, lookup
+    from tileinfer_b200.parts.norm import GatheredRows
+    T = DTYPES[dtype]
+    W, F, E, top = 72, 40, 6, 2
+    names = {"router": "router", "expert": "e{}.", "shared": "shared.", "gate": "gate", "up": "up", "down": "down"}
+    spec = FeedForwardSpec("routed_experts", "f.", W, F, names,
+                           {"experts": E, "top": top, "limit": 1.5, "scale_input": True, "sigmoid_slope": 1.702, "up_shift": 1.0,
+                            "shared_size": shared, "shared_limit": 0.8})
+    cls = lookup("feed_forward", "routed_experts")
+    g = torch.Generator().manual_seed(5 + shared)
+    tensors = {d.name: plain.rnd(torch.randn(d.shape, generator=g) * d.init[1] * 2, T) for d in cls.tensors(spec)}
+    assert ("f.shared.gate" in tensors) == bool(shared)
+    part = cls(spec, {k: v.to(T) for k, v in tensors.items()}, Runtime(T))
+    mlp = {"router": {"experts": E, "top": top}, "expert": {"ff": F, "limit": 1.5}}
+    if shared:
+        mlp["shared"] = {"ff": shared, "limit": 0.8}
+    for n in (1, 5, 300):
+        h = plain.rnd(torch.randn(n, W, generator=g), T)
+        margins = []
+        ref = plain.moe_ff(h, tensors, "f.", mlp, T, margins)
+        out = part.forward(h.to(T).cuda(), None)
+        assert isinstance(out, GatheredRows)
+        got = out.rows.float()[out.index.long()].sum(1).cpu()
+        sure = margins[0] > (0.02 if T == torch.bfloat16 else 1e-5)
+        tol = (2e-5 if T == torch.float32 else 2.0 ** -6) * float(ref.abs().max())
+        assert int(sure.sum()) >= n // 2 and float((got - ref)[sure].abs().max()) <= tol

@@ -635,7 +635,10 @@ int sm_count_cached() {
 int many_dispatch(void* y, long long ldy, const void* x, long long ldx, const void* W, long long w_rows, int n, int out, int in, int bn,
                   Params p, int* status, cudaStream_t stream) {
     p.N = n; p.K = in; p.M = out;
-    p.m_tiles = (out + BM - 1) / BM;
+    // Token tiles of 128 with 256 weight rows per block: the token operand staged for a k block feeds two MMAs (tiles of
+    // 128 x 128 are bound by the fill of shared memory).
+    const int mt = bn == 128 && out >= 2 * BM ? 2 : 1;
+    p.m_tiles = (out + mt * BM - 1) / (mt * BM);
     p.n_tiles = (n + bn - 1) / bn;
     p.k_blocks = (in + BK - 1) / BK;
     p.splits = 1;
@@ -654,7 +657,7 @@ int many_dispatch(void* y, long long ldy, const void* x, long long ldx, const vo
     const int sms = sm_count_cached();
     switch (bn) {
         case 256: return launch<256, 1>(y, mw, mx, my, p, sms, stream);
-        case 128: return launch<128, 1>(y, mw, mx, my, p, sms, stream);
+        case 128: return mt == 2 ? launch<128, 2>(y, mw, mx, my, p, sms, stream) : launch<128, 1>(y, mw, mx, my, p, sms, stream);
         case 64: return launch<64, 1>(y, mw, mx, my, p, sms, stream);
         case 32: return launch<32, 1>(y, mw, mx, my, p, sms, stream);
         default: return ti_fail("gemm_tcgen05: token tiles of %d", bn);

@@ -142,6 +142,17 @@ __global__ void expert_gather_kernel(T* __restrict__ xs, const T* h, const int* 
     }
     const float s = scale_input ? __ldcg(scores + p) : 1.0f;
     const T* src = h + (size_t)(p / top) * width;
+    constexpr int N = Vec16<T>::N;
+    if (width % N == 0 && ((((uintptr_t)src) | ((uintptr_t)dst)) & 15) == 0) {          // 16 bytes at a time; the same values
+        for (int i = threadIdx.x * N; i < width; i += blockDim.x * N) {
+            Vec16<T> v;
+            v.load_cg(src + i);
+#pragma unroll
+            for (int e = 0; e < N; ++e) v.v[e] = s * v.v[e];
+            v.store(dst + i);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_f32<T>(s * to_f32(__ldcg(src + i)));
 }
 

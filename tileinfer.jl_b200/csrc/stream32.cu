@@ -145,6 +145,93 @@ __global__ void branch_norm_add32_kernel(float* x, const T* delta, const float* 
     }
 }
 
+// The same for bfloat16 rows with four elements per thread and step: 16-byte accesses of the 32-bit stream, 8-byte
+// accesses of the bfloat16 rows. The order of a row's sums still depends on the row's size alone.
+__device__ __forceinline__ void load4(const bf16* p, float (&v)[4]) {
+    const uint2 t = __ldcg(reinterpret_cast<const uint2*>(p));
+    v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
+    v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
+}
+__device__ __forceinline__ void load4w(const bf16* __restrict__ p, float (&v)[4]) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
+    v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
+}
+__device__ __forceinline__ void store4(bf16* p, const float (&v)[4]) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const unsigned*>(&a), *reinterpret_cast<const unsigned*>(&b));
+}
+
+__global__ void branch_norm_add32_vec_kernel(float* x, const bf16* delta, const float* partials, int n_partials, size_t partial_stride,
+                                             const int* gather, int per_row, const bf16* __restrict__ w, int offset, float eps, float mult,
+                                             bf16* __restrict__ h, const bf16* __restrict__ w_out, int offset_out, float eps_out, int size) {
+    extern __shared__ float row_d[];
+    __shared__ float scratch[33];
+    float* row = x + (size_t)blockIdx.x * size;
+    float ss = 0.f;
+    pdl_enter();
+    for (int i = threadIdx.x * 4; i < size; i += blockDim.x * 4) {
+        float d[4];
+        if (partials != nullptr) {
+            const float* p = partials + (size_t)blockIdx.x * size + i;
+            float4 t = __ldcg(reinterpret_cast<const float4*>(p));
+            d[0] = t.x; d[1] = t.y; d[2] = t.z; d[3] = t.w;
+            for (int s = 1; s < n_partials; ++s) {
+                t = __ldcg(reinterpret_cast<const float4*>(p + (size_t)s * partial_stride));
+                d[0] += t.x; d[1] += t.y; d[2] += t.z; d[3] += t.w;
+            }
+        } else if (gather != nullptr) {
+            d[0] = d[1] = d[2] = d[3] = 0.f;
+            for (int j = 0; j < per_row; ++j) {
+                float v[4];
+                load4(delta + (size_t)__ldcg(gather + (size_t)blockIdx.x * per_row + j) * size + i, v);
+                d[0] += v[0]; d[1] += v[1]; d[2] += v[2]; d[3] += v[3];
+            }
+        } else {
+            load4(delta + (size_t)blockIdx.x * size + i, d);
+        }
+        *reinterpret_cast<float4*>(row_d + i) = make_float4(d[0], d[1], d[2], d[3]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ss = fmaf(d[e], d[e], ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)size + eps);
+    float ss2 = 0.f;
+    for (int i = threadIdx.x * 4; i < size; i += blockDim.x * 4) {
+        float g[4];
+        load4w(w + i, g);
+        const float4 xv = __ldcg(reinterpret_cast<const float4*>(row + i));
+        const float4 dv = *reinterpret_cast<const float4*>(row_d + i);
+        const float xs[4] = {xv.x, xv.y, xv.z, xv.w}, ds[4] = {dv.x, dv.y, dv.z, dv.w};
+        float v[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            v[e] = xs[e] + mult * (ds[e] * inv * (offset ? 1.0f + g[e] : g[e]));
+            ss2 = fmaf(v[e], v[e], ss2);
+        }
+        *reinterpret_cast<float4*>(row + i) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(row_d + i) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+    if (h == nullptr) return;
+    bf16* dst = h + (size_t)blockIdx.x * size;
+    float inv2 = 1.0f;
+    if (w_out != nullptr) {
+        ss2 = block_sum(ss2, scratch);
+        inv2 = 1.0f / sqrtf(ss2 / (float)size + eps_out);
+    }
+    for (int i = threadIdx.x * 4; i < size; i += blockDim.x * 4) {
+        const float4 t = *reinterpret_cast<const float4*>(row_d + i);
+        float v[4] = {t.x, t.y, t.z, t.w};
+        if (w_out != nullptr) {
+            float g[4];
+            load4w(w_out + i, g);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[e] = v[e] * inv2 * (offset_out ? 1.0f + g[e] : g[e]);
+        }
+        store4(dst + i, v);
+    }
+}
+
 extern "C" int ti_branch_norm_add32(float* x, const void* delta, const float* partials, int n_partials, long long partial_stride,
                                     const int* gather, int per_row, const void* w, int offset, float eps, float mult, void* h, const void* w_out, int offset_out,
                                     float eps_out, int n_rows, int size, int dtype, cudaStream_t stream) {
@@ -163,6 +250,13 @@ extern "C" int ti_branch_norm_add32(float* x, const void* delta, const float* pa
                 raised = true;
             }
         }
+        const bool vec = sizeof(T) == 2 && size % 4 == 0 && smem <= 48 * 1024 && aligned16(x) && (partials == nullptr || (aligned16(partials) && partial_stride % 4 == 0)) &&
+                         (((uintptr_t)delta | (uintptr_t)w | (uintptr_t)h | (uintptr_t)w_out) & 7) == 0;
+        if (vec) {
+            const int vt = size >= 2048 ? 256 : 128;
+            ti_launch(branch_norm_add32_vec_kernel, dim3(n_rows), dim3(vt), smem, stream, x, (const bf16*)delta, partials, n_partials,
+                      (size_t)partial_stride, gather, per_row, (const bf16*)w, offset, eps, mult, (bf16*)h, (const bf16*)w_out, offset_out, eps_out, size);
+        } else
         ti_launch(branch_norm_add32_kernel<T>, dim3(n_rows), dim3(threads), smem, stream, x, (const T*)delta, partials, n_partials,
                   (size_t)partial_stride, gather, per_row, (const T*)w, offset, eps, mult, (T*)h, (const T*)w_out, offset_out, eps_out, size);
     });
