@@ -375,4 +375,6 @@ def test_routed_units_alone(dtype, shared):
         got = out.rows.float()[out.index.long()].sum(1).cpu()
         sure = margins[0] > (0.02 if T == torch.bfloat16 else 1e-5)
         tol = (2e-5 if T == torch.float32 else 2.0 ** -6) * float(ref.abs().max())
-        assert int(sure.sum()) >= n // 2 and float((got - ref)[sure].abs().max()) <= tol
+        assert int(sure.sum()) >= n // 2
+        if bool(sure.any()):
+            assert float((got - ref)[sure].abs().max()) <= tol
