@@ -27,12 +27,32 @@ __global__ void gelu_kernel(T* out, const T* in, size_t count, int kind) {
     }
 }
 
+template <typename T>
+__global__ void gelu_vec_kernel(T* out, const T* in, size_t vecs, int kind) {
+    constexpr int N = Vec16<T>::N;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    pdl_enter();
+    for (; i < vecs; i += stride) {
+        Vec16<T> v;
+        v.load_cg(in + i * N);
+#pragma unroll
+        for (int e = 0; e < N; ++e) v.v[e] = kind == ACT_GELU_TANH ? gelu_tanh_value(v.v[e]) : gelu_erf_value(v.v[e]);
+        v.store(out + i * N);
+    }
+}
+
 extern "C" int ti_gelu(void* out, const void* in, long long count, int kind, int dtype, cudaStream_t stream) {
     if (count == 0) return 0;
     TI_REQUIRE(kind == ACT_GELU_ERF || kind == ACT_GELU_TANH, "gelu: unknown form %d", kind);
-    long long blocks = (count + 255) / 256;
-    if (blocks > ti_sm_count() * 16) blocks = ti_sm_count() * 16;
-    TI_DISPATCH_DTYPE(dtype, (ti_launch(gelu_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (T*)out, (const T*)in, (size_t)count, kind)));
+    TI_DISPATCH_DTYPE(dtype, {
+        constexpr int N = Vec16<T>::N;
+        const bool vec = count % N == 0 && aligned16(out) && aligned16(in);
+        long long blocks = ((vec ? count / N : count) + 255) / 256;
+        if (blocks > ti_sm_count() * 32) blocks = ti_sm_count() * 32;
+        if (vec) ti_launch(gelu_vec_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (T*)out, (const T*)in, (size_t)(count / N), kind);
+        else ti_launch(gelu_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (T*)out, (const T*)in, (size_t)count, kind);
+    });
     return ti_check_launch("gelu");
 }
 

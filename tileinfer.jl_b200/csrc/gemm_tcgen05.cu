@@ -56,7 +56,7 @@ struct Params {
     // g * w_group_rows. Batched (one matrix per head, all tokens): `batch` matrices, matrix b starts at weight row
     // b * w_batch_rows, reads the tokens' columns from b * x_batch_k on and writes the columns from b * y_batch_cols on.
     const int* groups;
-    int w_group_rows;
+    int w_group_rows, m_fastest;
     int batch, w_batch_rows, x_batch_k;
     long long y_batch_cols;
 };
@@ -94,9 +94,16 @@ struct TileIter {
     __device__ bool next(const Params& p) {
         if (id >= total) return false;
         int t = id;
-        n = t % n_tiles; t /= n_tiles;
-        split = t % p.splits; t /= p.splits;
-        m = t % p.m_tiles; b = t / p.m_tiles;
+        if (p.m_fastest) {
+            // One matrix per token tile, wide tiles: the blocks that run together take the weight tiles of the same few
+            // token tiles (they share those tokens in L2, and a matrix is streamed once, by the tiles of its rows; measured
+            // on 2,048 tokens x 6 of 34 matrices of 2,048 x 2,048: 130 against 137 us; with tiles of 64 rows it is slower).
+            m = t % p.m_tiles; n = t / p.m_tiles; split = 0; b = 0;
+        } else {
+            n = t % n_tiles; t /= n_tiles;
+            split = t % p.splits; t /= p.splits;
+            m = t % p.m_tiles; b = t / p.m_tiles;
+        }
         kb_lo = (int)((long long)p.k_blocks * split / p.splits);
         kb_hi = (int)((long long)p.k_blocks * (split + 1) / p.splits);
         rot = p.rotate ? (m * 7) % (kb_hi - kb_lo) : 0;
@@ -572,7 +579,7 @@ int gemm_dispatch(void* y, long long ldy, const void* x, long long ldx, const vo
     const int bn = n > 128 ? 256 : n > 64 ? 128 : n > 32 ? 64 : 32;
     Params p;
     p.N = n; p.K = in;
-    p.groups = nullptr; p.w_group_rows = 0; p.batch = 1; p.w_batch_rows = 0; p.x_batch_k = 0; p.y_batch_cols = 0;
+    p.groups = nullptr; p.w_group_rows = 0; p.m_fastest = 0; p.batch = 1; p.w_batch_rows = 0; p.x_batch_k = 0; p.y_batch_cols = 0;
     // Wide token tiles (more than 128 tokens): two SMs share a tile of 256 weight rows x 256 tokens
     // (cta_group::2): per MMA each SM fills 32 KB of shared memory instead of 48 KB, both accumulator buffers
     // stay, so the epilogue (xIELU included) overlaps the next tile, and a stage of 128 of k means one barrier
@@ -635,6 +642,7 @@ int sm_count_cached() {
 int many_dispatch(void* y, long long ldy, const void* x, long long ldx, const void* W, long long w_rows, int n, int out, int in, int bn,
                   Params p, int* status, cudaStream_t stream) {
     p.N = n; p.K = in; p.M = out;
+    p.m_fastest = p.groups != nullptr && bn >= 128;
     // Token tiles of 128 with 256 weight rows per block: the token operand staged for a k block feeds two MMAs (tiles of
     // 128 x 128 are bound by the fill of shared memory).
     const int mt = bn == 128 && out >= 2 * BM ? 2 : 1;

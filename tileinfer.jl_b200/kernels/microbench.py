@@ -27,7 +27,7 @@ import sys
 
 import torch
 
-from . import fast
+from . import fast, ops
 from .library import check, lib
 
 APERTUS_8B_LAYER = dict(hidden=4096, heads=32, kv_heads=8, head_dim=128, intermediate=21504, vocab=131072)
@@ -91,6 +91,46 @@ def bench_product(kind, out, k, n, splits, epilogue, once, tile=0, Ws=None, quie
         return ms
     print(f"{kind} out={out} in={k} tokens={n} splits={splits} epilogue={epilogue}: {ms * 1e3:.1f} us, "
           f"{out * k * 2 / ms / 1e6:.0f} GB/s of weights, {2 * n * out * k / ms / 1e9:.1f} TFLOP/s")
+
+
+def bench_grouped(tokens, experts, top, always, out, k, once):
+    """The grouped product (one matrix per expert) on rows routed at random: ``tokens`` x (``top`` of ``experts`` + ``always``
+    units that every token takes), matrices [out, k]. Several sets of matrices, so that weights come from memory."""
+    units, per_token = experts + always, top + always
+    g = torch.Generator(device="cuda").manual_seed(0)
+    ids = torch.empty(tokens, per_token, dtype=torch.int32, device="cuda")
+    ids[:, :top] = torch.rand(tokens, experts, device="cuda", generator=g).topk(top, dim=1).indices.int()
+    for a in range(always):
+        ids[:, top + a] = experts + a
+    pairs = tokens * per_token
+    tile = fast.grouped_tile(pairs, units)
+    max_tiles, rows = ops.expert_plan_sizes(pairs, units, tile)
+    pair_row = torch.empty(pairs, dtype=torch.int32, device="cuda")
+    row_pair = torch.empty(rows, dtype=torch.int32, device="cuda")
+    plan = torch.empty(1 + max_tiles, dtype=torch.int32, device="cuda")
+    ops.expert_plan(ids, units, tile, pair_row, row_pair, plan)
+    used = int(plan[0].item())
+    touched = len(set(plan[1:1 + used].tolist()))
+    x = torch.randn(rows, k, device="cuda").to(torch.bfloat16)
+    y = torch.empty(rows, out, dtype=torch.bfloat16, device="cuda")
+    sets = max(2, min(8, int(400e6 // (units * out * k * 2)) + 1))
+    Ws = [(torch.randn(units, out, k, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(sets)]
+
+    def call(W):
+        if not fast.grouped_linear(y, x, W, plan, tile):
+            raise RuntimeError("the tensor-core grouped product refused these sizes")
+    if once:
+        for W in Ws[:3]:
+            call(W)
+        torch.cuda.synchronize()
+        print("launched", min(3, len(Ws)), "grouped products")
+        return
+    ms = _graph_time([(lambda W=W: call(W)) for W in Ws])
+    fast.check_status()
+    flops_real, flops_padded = 2.0 * pairs * out * k, 2.0 * used * tile * out * k
+    print(f"grouped tokens={tokens} experts={experts} top={top} always={always} out={out} in={k}: tile {tile}, {used} tiles "
+          f"({used * tile} rows for {pairs} pairs), {ms * 1e3:.1f} us, {flops_real / ms / 1e9:.1f} TFLOP/s of the pairs' work, "
+          f"{flops_padded / ms / 1e9:.1f} with padding, {touched * out * k * 2 / ms / 1e6:.0f} GB/s of the {touched} matrices in use")
 
 
 def bench_decode_attention(batch, context, once, splits=0, heads=32, kv_heads=8, head_dim=128):
@@ -300,7 +340,10 @@ def timeline(batch, layers, cached=1023, prefill_tokens=0, shape=None, config=No
 
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="microbench")
-    ap.add_argument("what", choices=["gemv", "gemm", "gemmd", "decode", "prefill", "inputs", "addnorm", "sampling", "timeline"])
+    ap.add_argument("what", choices=["gemv", "gemm", "gemmd", "grouped", "decode", "prefill", "inputs", "addnorm", "sampling", "timeline"])
+    ap.add_argument("--experts", type=int, default=32, help="grouped: routed experts")
+    ap.add_argument("--top", type=int, default=4, help="grouped: experts per token")
+    ap.add_argument("--always", type=int, default=2, help="grouped: units that every token takes besides")
     ap.add_argument("--out", type=int, default=21504)
     ap.add_argument("--in", dest="k", type=int, default=4096)
     ap.add_argument("--tokens", type=int, default=1)
@@ -320,6 +363,8 @@ def main(argv=None):
         fast.DECODE_PRODUCT_MAX_TOKENS = 0
     if a.what in ("gemv", "gemm", "gemmd"):
         bench_product(a.what, a.out, a.k, a.tokens, max(1, a.splits), a.epilogue, a.once, tile=a.tile)
+    elif a.what == "grouped":
+        bench_grouped(a.tokens, a.experts, a.top, a.always, a.out, a.k, a.once)
     elif a.what == "decode":
         bench_decode_attention(a.batch, a.context, a.once, a.splits)
     elif a.what == "prefill":
