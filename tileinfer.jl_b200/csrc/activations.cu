@@ -11,10 +11,6 @@
 #define ACT_GELU_ERF 0
 #define ACT_GELU_TANH 1
 
-__device__ __forceinline__ float gelu_erf_value(float z) { return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f)); }
-__device__ __forceinline__ float gelu_tanh_value(float z) {
-    return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
-}
 
 template <typename T>
 __global__ void gelu_kernel(T* out, const T* in, size_t count, int kind) {

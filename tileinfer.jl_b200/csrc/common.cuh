@@ -153,6 +153,18 @@ __device__ __forceinline__ void xielu_bf16_pair(float s0, float s1, const XieluP
     hi = (x1 > 0.f ? P : N) >> 16;
 }
 
+// GELU in its exact form 0.5 x (1 + erf(x / sqrt 2)) and in its tanh form 0.5 x (1 + tanh(sqrt(2 / pi) (x + 0.044715 x^3))).
+// As a product's epilogue (codes TI_EPI_GELU_ERF / TI_EPI_GELU_TANH) it is applied to the sum rounded to the storage type.
+#define TI_EPI_GELU_ERF 4
+#define TI_EPI_GELU_TANH 5
+__device__ __forceinline__ float gelu_erf_value(float z) { return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f)); }
+__device__ __forceinline__ float gelu_tanh_value(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+}
+__device__ __forceinline__ float gelu_epilogue(float v, int epilogue) {
+    return epilogue == TI_EPI_GELU_TANH ? gelu_tanh_value(v) : gelu_erf_value(v);
+}
+
 // 16 bytes of elements, widened to float on load and rounded once on store.
 template <typename T> struct Vec16;
 template <> struct Vec16<float> {

@@ -71,6 +71,7 @@ __global__ void __launch_bounds__(256) gemm_plain_kernel(void* __restrict__ y, l
             if (c >= out) continue;
             float v = rnd<T>(acc[i][j]);
             if (epilogue == TI_EPI_XIELU) v = xielu_value<T>(v, act);
+            if (epilogue >= TI_EPI_GELU_ERF) v = gelu_epilogue(v, epilogue);
             if (epilogue == TI_EPI_F32_OUT) ((float*)y)[(size_t)r * ldy + c] = v;
             else ((T*)y)[(size_t)r * ldy + c] = from_f32<T>(v);
         }
@@ -161,6 +162,7 @@ __global__ void __launch_bounds__(256) gemm_plain_wide_kernel(void* __restrict__
             if (c >= out) continue;
             float v = rnd<T>(acc[i][j]);
             if (epilogue == TI_EPI_XIELU) v = xielu_value<T>(v, act);
+            if (epilogue >= TI_EPI_GELU_ERF) v = gelu_epilogue(v, epilogue);
             if (epilogue == TI_EPI_F32_OUT) ((float*)y)[(size_t)r * ldy + c] = v;
             else ((T*)y)[(size_t)r * ldy + c] = from_f32<T>(v);
         }
@@ -246,6 +248,7 @@ __global__ void __launch_bounds__(GV_ROWS * GV_SLOTS) gemv_plain_kernel(void* __
         if (t >= n) continue;
         float v = rnd<T>(acc[j]);
         if (epilogue == TI_EPI_XIELU) v = xielu_value<T>(v, act);
+            if (epilogue >= TI_EPI_GELU_ERF) v = gelu_epilogue(v, epilogue);
         if (epilogue == TI_EPI_F32_OUT) ((float*)y)[(size_t)t * ldy + c] = v;
         else ((T*)y)[(size_t)t * ldy + c] = from_f32<T>(v);
     }
@@ -325,6 +328,7 @@ __global__ void __launch_bounds__(GV_ROWS * GV_SLOTS) gemv_plain_pipe_kernel(voi
         if (t >= n) continue;
         float v = rnd<T>(acc[j]);
         if (epilogue == TI_EPI_XIELU) v = xielu_value<T>(v, act);
+            if (epilogue >= TI_EPI_GELU_ERF) v = gelu_epilogue(v, epilogue);
         if (epilogue == TI_EPI_F32_OUT) ((float*)y)[(size_t)t * ldy + c] = v;
         else ((T*)y)[(size_t)t * ldy + c] = from_f32<T>(v);
     }
@@ -351,7 +355,7 @@ extern "C" int ti_gemm_plain(void* y, long long ldy, const void* x, long long ld
                              cudaStream_t stream) {
     if (n == 0) return 0;
     TI_REQUIRE(n > 0 && out > 0 && in > 0, "gemm: bad sizes n=%d out=%d in=%d", n, out, in);
-    TI_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm: unknown epilogue %d", epilogue);
+    TI_REQUIRE((epilogue >= 0 && epilogue <= 2) || epilogue == TI_EPI_GELU_ERF || epilogue == TI_EPI_GELU_TANH, "gemm: unknown epilogue %d", epilogue);
     dim3 grid((out + GP_BN - 1) / GP_BN, (n + GP_BM - 1) / GP_BM);
     TI_REQUIRE(grid.y <= 65535, "gemm: too many rows (%d) for one launch", n);
     XieluParams act{alpha_p, alpha_n, beta, eps};

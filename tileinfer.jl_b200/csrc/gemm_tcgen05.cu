@@ -129,7 +129,7 @@ __device__ __forceinline__ void epilogue_rows(unsigned t_row, int m_first, int l
         tmem_ld_wait();
         // All values of the chunk first, without branches (one warp per scheduler runs this: only
         // independent elements in flight hide the latency of the arithmetic), then the stores.
-        if (p.epilogue >= EPI_F32) {
+        if (p.epilogue == EPI_F32 || p.epilogue == EPI_PARTIAL) {
             if (m < p.M) {
                 float* yf = (float*)y + ((size_t)(p.epilogue == EPI_PARTIAL ? split : 0) * p.N + n0 + c) * p.ldy + y_col0 + m;
 #pragma unroll
@@ -146,6 +146,10 @@ __device__ __forceinline__ void epilogue_rows(unsigned t_row, int m_first, int l
             const float s0 = __uint_as_float(r[j]), s1 = __uint_as_float(r[j + 1]);
             if (p.epilogue == EPI_XIELU) {
                 xielu_bf16_pair(s0, s1, act, o[j], o[j + 1]);
+            } else if (p.epilogue >= TI_EPI_GELU_ERF) {
+                const __nv_bfloat162 q = __floats2bfloat162_rn(gelu_epilogue(rnd<bf16>(s0), p.epilogue), gelu_epilogue(rnd<bf16>(s1), p.epilogue));
+                const unsigned bits = *reinterpret_cast<const unsigned*>(&q);
+                o[j] = bits & 0xffffu; o[j + 1] = bits >> 16;
             } else {
                 const __nv_bfloat162 q = __floats2bfloat162_rn(s0, s1);
                 const unsigned bits = *reinterpret_cast<const unsigned*>(&q);
@@ -612,7 +616,7 @@ int gemm_dispatch(void* y, long long ldy, const void* x, long long ldx, const vo
     // tile walks its k range from a start of its own (a function of the tile alone: a token's result does not
     // depend on the step it is in). With many tokens the tiles of a row of blocks share lines on purpose.
     p.rotate = n <= 64;
-    p.tma_out = bn >= 128 && (epilogue == EPI_NONE || epilogue == EPI_XIELU) && ldy % 8 == 0 && !((uintptr_t)y & 15);
+    p.tma_out = bn >= 128 && (epilogue == EPI_NONE || epilogue == EPI_XIELU || epilogue >= TI_EPI_GELU_ERF) && ldy % 8 == 0 && !((uintptr_t)y & 15);
     if (p.tma_out) {
         if (int rc = tensor_map(&my, y, n, out, ldy, 32, 32)) return rc;
     } else {
@@ -718,7 +722,7 @@ extern "C" int ti_gemm_tcgen05(void* y, long long ldy, const void* x, long long 
         ti_fail("gemm_tcgen05 needs 16-byte aligned rows: in=%d, ldx=%lld", in, ldx);
         return 2;
     }
-    TI_REQUIRE(epilogue >= 0 && epilogue <= 3, "gemm_tcgen05: unknown epilogue %d", epilogue);
+    TI_REQUIRE(epilogue >= 0 && epilogue <= TI_EPI_GELU_TANH, "gemm_tcgen05: unknown epilogue %d", epilogue);
     TI_REQUIRE(status != nullptr, "gemm_tcgen05: status word missing");
     static int sm_count = 0;
     if (!sm_count) {

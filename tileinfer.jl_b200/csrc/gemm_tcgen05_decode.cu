@@ -220,7 +220,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_decode_kernel(const _
                     if (count == 32) tmem_ld32(t_row + c, r); else tmem_ld16(t_row + c, r);
                     tmem_ld_wait();
                     const int m = m0 + c;
-                    if (p.epilogue >= EPI_F32) {
+                    if (p.epilogue == EPI_F32 || p.epilogue == EPI_PARTIAL) {
                         float v[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
@@ -238,6 +238,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_decode_kernel(const _
                             const float s0 = __uint_as_float(r[j]), s1 = __uint_as_float(r[j + 1]);
                             if (p.epilogue == EPI_XIELU) {
                                 xielu_bf16_pair(s0, s1, act, o[j], o[j + 1]);
+                            } else if (p.epilogue >= TI_EPI_GELU_ERF) {
+                                const __nv_bfloat162 q = __floats2bfloat162_rn(gelu_epilogue(rnd<bf16>(s0), p.epilogue),
+                                                                               gelu_epilogue(rnd<bf16>(s1), p.epilogue));
+                                const unsigned bits = *reinterpret_cast<const unsigned*>(&q);
+                                o[j] = bits & 0xffffu; o[j + 1] = bits >> 16;
                             } else {
                                 const __nv_bfloat162 q = __floats2bfloat162_rn(s0, s1);
                                 const unsigned bits = *reinterpret_cast<const unsigned*>(&q);
@@ -339,7 +344,7 @@ extern "C" int ti_gemm_tcgen05_decode(void* y, long long ldy, const void* x, lon
         ti_fail("gemm_tcgen05_decode takes up to %d tokens and 16-byte aligned rows: n=%d, in=%d, ldx=%lld", 2 * BMT, n, in, ldx);
         return 2;
     }
-    TI_REQUIRE(epilogue >= 0 && epilogue <= 3, "gemm_tcgen05_decode: unknown epilogue %d", epilogue);
+    TI_REQUIRE(epilogue >= 0 && epilogue <= TI_EPI_GELU_TANH, "gemm_tcgen05_decode: unknown epilogue %d", epilogue);
     TI_REQUIRE(status != nullptr, "gemm_tcgen05_decode: status word missing");
     const int sm_count = device_sm_count();
     if (nt <= 0) plan(n, out, in, 1, sm_count, &nt, &splits);

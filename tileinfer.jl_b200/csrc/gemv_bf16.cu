@@ -126,6 +126,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_bf16_kernel(const bf16* __
         }
         float v = rnd<bf16>(s);
         if (epilogue == GV_EPI_XIELU) v = xielu_value<bf16>(v, act);
+        if (epilogue >= TI_EPI_GELU_ERF) v = gelu_epilogue(v, epilogue);
         if (epilogue == GV_EPI_F32_OUT) ((float*)y)[(size_t)col * ldy + row] = v;
         else ((bf16*)y)[(size_t)col * ldy + row] = __float2bfloat16_rn(v);
     }
@@ -140,7 +141,7 @@ extern "C" int ti_gemv_bf16(void* y, long long ldy, const void* x, long long ldx
     TI_REQUIRE(in % 8 == 0 && ldx % 8 == 0, "gemv: in=%d and the row stride of x (%lld) must be multiples of 8", in, ldx);
     TI_REQUIRE(((uintptr_t)W % 16 == 0) && ((uintptr_t)x % 16 == 0), "gemv: operands must be 16-byte aligned");
     TI_REQUIRE(splits >= 1 && (splits == 1 || epilogue == GV_EPI_PARTIAL), "gemv: a split product leaves partial sums");
-    TI_REQUIRE(epilogue >= 0 && epilogue <= 3, "gemv: unknown epilogue %d", epilogue);
+    TI_REQUIRE(epilogue >= 0 && epilogue <= TI_EPI_GELU_TANH, "gemv: unknown epilogue %d", epilogue);
     dim3 grid((out + 15) / 16, splits);
     XieluParams act{alpha_p, alpha_n, beta, eps};
     if (n <= 8)

@@ -68,11 +68,11 @@ class GeluMLP(FeedForward):
         n, p = spec.tensor_names, spec.prefix
         self.up = Linear(rt.param(tensors[p + n["up"]]), rt, "up")
         self.down = Linear(rt.param(tensors[p + n["down"]]), rt, "down")
-        kinds = {"gelu_erf": ops.ACT_GELU_ERF, "gelu_tanh": ops.ACT_GELU_TANH}
+        kinds = {"gelu_erf": ops.EPI_GELU_ERF, "gelu_tanh": ops.EPI_GELU_TANH}
         act = spec.options.get("activation", "gelu_erf")
         if act not in kinds:
             raise ValueError(f"gelu_mlp: activation {act!r} (known: {', '.join(kinds)})")
-        self.kind = kinds[act]
+        self.epilogue = kinds[act]                # the activation is the up projection's epilogue
 
     @classmethod
     def tensors(cls, spec: FeedForwardSpec):
@@ -83,7 +83,6 @@ class GeluMLP(FeedForward):
     def forward(self, h, step):
         n = h.shape[0]
         act = self.rt.buffer("feed_forward.act", (n, self.spec.intermediate_size))
-        self.up.forward(h, act)
-        ops.gelu(act, act, self.kind)
+        self.up.forward(h, act, self.epilogue)
         out = self.rt.buffer("feed_forward.delta", (n, self.spec.hidden_size))
         return self.down.forward(act, out, allow_partials=True)
