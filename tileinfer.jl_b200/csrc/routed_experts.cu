@@ -129,22 +129,16 @@ extern "C" int ti_expert_plan(const int* ids, int pairs, int experts, int tile, 
     return ti_check_launch("expert_plan");
 }
 
+// One row of xs for a pair: xs[pair_row[p]] = T(score * h[token]) (or T(h[token])). Padding rows are left as they are:
+// a row's results depend on that row alone, and nobody reads a padding row's.
 template <typename T>
-__global__ void expert_gather_kernel(T* __restrict__ xs, const T* h, const int* row_pair, const float* scores, int top, int width,
-                                     int scale_input) {
-    const int row = blockIdx.x;
-    pdl_enter();
-    const int p = __ldcg(row_pair + row);
+__device__ __forceinline__ void gather_pair_row(T* __restrict__ xs, const T* h, int row, int p, float s, int per_token, int width,
+                                                int first_thread, int threads) {
+    const T* src = h + (size_t)(p / per_token) * width;
     T* dst = xs + (size_t)row * width;
-    if (p < 0) {                                            // a padding row
-        for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_f32<T>(0.f);
-        return;
-    }
-    const float s = scale_input ? __ldcg(scores + p) : 1.0f;
-    const T* src = h + (size_t)(p / top) * width;
     constexpr int N = Vec16<T>::N;
     if (width % N == 0 && ((((uintptr_t)src) | ((uintptr_t)dst)) & 15) == 0) {          // 16 bytes at a time; the same values
-        for (int i = threadIdx.x * N; i < width; i += blockDim.x * N) {
+        for (int i = first_thread * N; i < width; i += threads * N) {
             Vec16<T> v;
             v.load_cg(src + i);
 #pragma unroll
@@ -153,14 +147,22 @@ __global__ void expert_gather_kernel(T* __restrict__ xs, const T* h, const int* 
         }
         return;
     }
-    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_f32<T>(s * to_f32(__ldcg(src + i)));
+    for (int i = first_thread; i < width; i += threads) dst[i] = from_f32<T>(s * to_f32(__ldcg(src + i)));
 }
 
-extern "C" int ti_expert_gather(void* xs, const void* h, const int* row_pair, const float* scores, int rows, int top, int width,
+template <typename T>
+__global__ void expert_gather_kernel(T* __restrict__ xs, const T* h, const int* pair_row, const float* scores, int per_token, int width,
+                                     int scale_input) {
+    const int p = blockIdx.x;
+    pdl_enter();
+    gather_pair_row(xs, h, __ldcg(pair_row + p), p, scale_input ? __ldcg(scores + p) : 1.0f, per_token, width, (int)threadIdx.x, (int)blockDim.x);
+}
+
+extern "C" int ti_expert_gather(void* xs, const void* h, const int* pair_row, const float* scores, int pairs, int per_token, int width,
                                 int scale_input, int dtype, cudaStream_t stream) {
-    if (rows == 0) return 0;
-    TI_DISPATCH_DTYPE(dtype, (ti_launch(expert_gather_kernel<T>, dim3(rows), dim3(width >= 1024 ? 256 : 128), 0, stream, (T*)xs, (const T*)h,
-                                        row_pair, scores, top, width, scale_input)));
+    if (pairs == 0) return 0;
+    TI_DISPATCH_DTYPE(dtype, (ti_launch(expert_gather_kernel<T>, dim3(pairs), dim3(width >= 1024 ? 256 : 128), 0, stream, (T*)xs, (const T*)h,
+                                        pair_row, scores, per_token, width, scale_input)));
     return ti_check_launch("expert_gather");
 }
 

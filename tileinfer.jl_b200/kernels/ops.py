@@ -341,10 +341,11 @@ def expert_plan(ids, experts, tile, pair_row, row_pair, plan):
                                plan.data_ptr(), _stream()), "expert_plan")
 
 
-def expert_gather(xs, h, row_pair, scores, top, scale_input=True):
-    _need(xs, "xs"); _need(h, "h", xs.dtype); _need(row_pair, "row_pair", torch.int32); _need(scores, "scores", torch.float32)
-    check(lib().ti_expert_gather(xs.data_ptr(), h.data_ptr(), row_pair.data_ptr(), scores.data_ptr(), xs.shape[0], top, xs.shape[1],
-                                 int(bool(scale_input)), dtype_code(xs.dtype), _stream()), "expert_gather")
+def expert_gather(xs, h, pair_row, scores, per_token, scale_input=True):
+    """xs[pair_row[p]] = score[p] * h[p // per_token] (or h[...] itself) for every pair p; padding rows are not touched."""
+    _need(xs, "xs"); _need(h, "h", xs.dtype); _need(pair_row, "pair_row", torch.int32); _need(scores, "scores", torch.float32)
+    check(lib().ti_expert_gather(xs.data_ptr(), h.data_ptr(), pair_row.data_ptr(), scores.data_ptr(), pair_row.numel(), per_token,
+                                 xs.shape[1], int(bool(scale_input)), dtype_code(xs.dtype), _stream()), "expert_gather")
 
 
 def grouped_gemm(y, x, w, plan, tile, gated=False, limits=None, slope=0.0, shift=0.0):
@@ -369,3 +370,4 @@ def expert_combine(out, y, pair_row, scores, shared, top, scale_output=False):
     n, width = out.shape
     check(lib().ti_expert_combine(out.data_ptr(), y.data_ptr(), pair_row.data_ptr(), scores.data_ptr(), _ptr(shared), n, top, width,
                                   int(bool(scale_output)), dtype_code(out.dtype), _stream()), "expert_combine")
+

@@ -95,18 +95,18 @@ class RoutedExperts(FeedForward):
             from ..kernels import fast
         ids = rt.buffer("experts.ids", (n, per_token), torch.int32)
         scores = rt.buffer("experts.scores", (n, per_token), torch.float32)
-        logits = None
-        if fast is not None:                     # the router's 32-bit sums from a product kernel, where one takes the sizes
-            logits = fast.linear_f32(self.router_linear, h, rt.buffer("experts.logits", (n, E), torch.float32))
-        ops.router_topk(h, self.router, top, ids, scores, logits, always=self.always)
         tile = fast.grouped_tile(pairs, self.units) if fast is not None else ops.EXPERT_TILE_ROWS
         max_tiles, rows = ops.expert_plan_sizes(pairs, self.units, tile)
         pair_row = rt.buffer("experts.pair_row", (n, per_token), torch.int32)
         row_pair = rt.buffer("experts.row_pair", (rows,), torch.int32)
         plan = rt.buffer("experts.plan", (1 + max_tiles,), torch.int32)
-        ops.expert_plan(ids, self.units, tile, pair_row, row_pair, plan)
         xs = rt.buffer("experts.rows", (rows, W))
-        ops.expert_gather(xs, h, row_pair, scores, per_token, self.scale_input)
+        logits = None
+        if fast is not None:                     # the router's 32-bit sums from a product kernel, where one takes the sizes
+            logits = fast.linear_f32(self.router_linear, h, rt.buffer("experts.logits", (n, E), torch.float32))
+        ops.router_topk(h, self.router, top, ids, scores, logits, always=self.always)
+        ops.expert_plan(ids, self.units, tile, pair_row, row_pair, plan)
+        ops.expert_gather(xs, h, pair_row, scores, per_token, self.scale_input)
         act = rt.buffer("experts.act", (rows, F))
         gu = rt.buffer("experts.gate_up", (rows, 2 * F))
         if fast is not None and fast.grouped_linear(gu, xs, self.gate_up, plan, tile):

@@ -51,10 +51,10 @@ class GatedEmbedding(TokenInput):
 
     def forward(self, h, step):
         n = h.shape[0]
+        y = self.rt.buffer("token_input.out", (n, self.spec.hidden_size))
         g = self.rt.buffer("token_input.gate", (n, self.spec.dim))
         self.gate.forward(h, g)
         ops.gated_token_embedding(g, self.table, step.token_ids, self.spec.first_column)
-        y = self.rt.buffer("token_input.out", (n, self.spec.hidden_size))
         return self.proj.forward(g, y)
 
 
