@@ -100,3 +100,15 @@ def test_plain_pieces():
     assert bad.tolist() == [False, False] + [True] * 8                                 # a layer without window: to the end
     last = plain.unsure_positions(cfg, [(2, margins[0][1])], 10, 0.01)
     assert last.tolist() == [False, False, True] + [False] * 7
+
+
+def test_command_line_writes_a_model_folder_of_this_design(tmp_path, capsys):
+    from tileinfer_b200.cli import cli
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(vc.CASE_B))
+    out = tmp_path / "model"
+    assert cli(["random", str(cfg), str(out), "--seed", "9"]) == 0 and "wrote" in capsys.readouterr().out
+    again, W = plain.load_folder(str(out))
+    assert again["architecture"] == "Vogilix" and again["layers"] == vc.CASE_B["layers"]
+    assert "residual_mult" in again and again["residual_mult"] == 1.0          # what the file left out is written with its default
+    assert W["l1.mlp.e3.up"].shape == (72, 128) and "l1.mlp.shared.up" not in W and "side.embed" not in W
