@@ -4,13 +4,15 @@
 //                   the `top` largest (ties to the smaller index) -> ids [n, top], scores [n, top]
 //   expert_plan     the (token, choice) pairs grouped by expert: a row for every pair in expert order, every expert's rows
 //                   padded to whole tiles, and the expert of every tile; one block, counts in shared memory
-//   expert_gather   xs[row] = T(score * h[token]) (the score scales an expert's INPUT) or T(h[token]); zeros in padding rows
+//   expert_gather   xs[row of the pair] = T(score * h[token]) (the score scales an expert's INPUT) or T(h[token]); padding rows
+//                   are left as they are (a row's results depend on that row alone, and nobody reads a padding row's)
 //   grouped_gemm    for every tile: y[row, :] = W[expert] xs[row, :] on the CUDA cores (the 32-bit path, and sizes the
 //                   tensor-core kernel refuses; csrc/gemm_tcgen05.cu has the tensor-core form); as a gated unit W[expert]
 //                   holds gate rows then up rows and y = a * sigmoid(slope * a) * (b + shift), a = min(gate, limit),
 //                   b = clamp(up, -limit, limit)
 //   expert_combine  out[token] = sum over the token's choices, in choice order, of y[row(token, choice)] (times the score
-//                   where it scales the OUTPUT) + the shared unit's row, in 32-bit, rounded once
+//                   where it scales the OUTPUT) + a shared row, in 32-bit, rounded once (where the score scales the INPUT the
+//                   stream's update adds the rows up itself: csrc/stream32.cu)
 //
 // Nothing here reads a count on the host: grids are sized by upper bounds and blocks beyond the device-side
 // counts leave at once, so a step with a routed feed-forward can be captured in a CUDA graph.
@@ -81,8 +83,8 @@ extern "C" int ti_router_topk(const void* h, const void* wr, const float* logits
 }
 
 // The plan of a step: the pairs grouped by expert, every expert's rows padded to whole tiles of `tile` rows, so that a
-// tile holds rows of one expert only (tensor-core kernels then treat a tile like any other; padding rows hold zeros and
-// nobody reads their results). plan[0] = tiles in use, plan[1 + t] = the expert of tile t. pair_row[pair] = the pair's
+// tile holds rows of one expert only (tensor-core kernels then treat a tile like any other; nobody reads the results of
+// padding rows). plan[0] = tiles in use, plan[1 + t] = the expert of tile t. pair_row[pair] = the pair's
 // row; row_pair[row] = the row's pair, or -1 for padding, for all `capacity` rows.
 __global__ void expert_plan_kernel(const int* ids, int pairs, int experts, int tile, int capacity, int* __restrict__ pair_row,
                                    int* __restrict__ row_pair, int* __restrict__ plan) {
