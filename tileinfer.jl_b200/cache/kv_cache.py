@@ -29,6 +29,7 @@ device and zeroes fresh pages with one kernel; this module allocates the storage
 from __future__ import annotations
 
 import ctypes
+import dataclasses
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -52,6 +53,16 @@ class LayerCache:
     v: Optional[torch.Tensor] = None
     state: Optional[torch.Tensor] = None    # [slots, *shape]
     extra: object = None                    # whatever a registered kind of its own hands to its mixer
+
+
+def _merge_views(a: Optional[LayerCache], b: LayerCache, layer: int) -> LayerCache:
+    """One view for a layer that asked for pages and for a state: the paged view with the state's tensor attached."""
+    if a is None:
+        return b
+    paged, other = (a, b) if a.k is not None else (b, a)
+    if paged.k is None or other.k is not None or paged.state is not None or other.state is None:
+        raise ValueError(f"layer {layer} asks for two storages of the same kind")
+    return dataclasses.replace(paged, state=other.state)
 
 
 # The kinds of storage a CacheRequest can name. A group class has
@@ -233,8 +244,9 @@ class _Slots:
 
 
 class Cache:
-    """``requests[i]`` is layer i's CacheRequest (None: the layer keeps nothing; it may read another
-    layer's storage, see ``share``). ``max_tokens`` is the most positions live sequences hold together,
+    """``requests[i]`` is layer i's CacheRequest, or several of different kinds (pages of keys and values and a small
+    state, for one), or None (the layer keeps nothing; it may read the pages of another layer, see ``share``, which
+    leaves a state of its own in place). ``max_tokens`` is the most positions live sequences hold together,
     each sequence rounded up to whole pages. ``max_step_tokens``: the most tokens that run between two
     calls of ``advance`` (it sizes the pools of groups with a window; None: sized like the others)."""
 
@@ -252,10 +264,12 @@ class Cache:
         self.max_step_tokens = max_step_tokens
         self.release_granule = release_granule
         by_key: Dict[tuple, List[int]] = {}
+        first_request: Dict[tuple, CacheRequest] = {}
         for i, r in enumerate(requests):
-            if r is not None:
-                by_key.setdefault(r.group_key(), []).append(i)
-        kinds = {requests[layers[0]].kind for layers in by_key.values()}
+            for one in ([] if r is None else [r] if isinstance(r, CacheRequest) else list(r)):
+                by_key.setdefault(one.group_key(), []).append(i)
+                first_request.setdefault(one.group_key(), one)
+        kinds = {r.kind for r in first_request.values()}
         for kind in sorted(kinds):
             if kind not in _GROUP_KINDS:
                 raise ValueError(f"unknown cache kind {kind!r} (registered: {', '.join(sorted(_GROUP_KINDS))})")
@@ -265,13 +279,15 @@ class Cache:
         self.groups = []
         self._layer_view: Dict[int, LayerCache] = {}
         for key, layers in by_key.items():
-            r = requests[layers[0]]
+            r = first_request[key]
             g = _GROUP_KINDS[r.kind].create(self, len(self.groups), r, layers)
             for l, view in zip(layers, g.views()):
-                self._layer_view[l] = view
+                self._layer_view[l] = _merge_views(self._layer_view.get(l), view, l)
             self.groups.append(g)
         for reader, source in (share or {}).items():
-            self._layer_view[reader] = self._layer_view[source]
+            # The reader sees the source's pages; a state is never shared (the reader's own, if it asked for one, stays).
+            own = self._layer_view.get(reader)
+            self._layer_view[reader] = dataclasses.replace(self._layer_view[source], state=own.state if own is not None else None)
         self.paged_groups = [g for g in self.groups if g.paged]
         self.state_groups = [g for g in self.groups if not g.paged]
         self.windowed_groups = [g for g in self.paged_groups if g.window]

@@ -4,3 +4,4 @@ from .registry import (Architecture, config_from_dict, load_config, register_arc
 from .spec import (FeedForwardSpec, LayerSpec, Llama3RopeScaling, MixerSpec, ModelSpec, NormSpec, PositionSpec,
                    TensorDecl, TokenInputSpec)
 from .vogilix import VogilixConfig
+from .zudepel import ZudepelConfig

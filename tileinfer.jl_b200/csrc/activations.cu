@@ -142,3 +142,27 @@ extern "C" int ti_gated_unit_limit(void* y, const void* gu, int n, int ff, float
     });
     return ti_check_launch("gated_unit_limit");
 }
+
+// A gated unit's inner activation without a clamp: y[t, j] = act(gu[t, j]) * gu[t, ff + j], act = SiLU (kind 0) or the tanh
+// form of GELU (kind 1); gate rows first, then up rows. 32-bit arithmetic, one rounding.
+template <typename T>
+__global__ void gated_act_kernel(T* __restrict__ y, const T* gu, int ff, int kind, size_t count) {
+    pdl_enter();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / ff;
+        const int j = (int)(i % ff);
+        const float g = to_f32(__ldcg(gu + t * 2 * ff + j)), u = to_f32(__ldcg(gu + t * 2 * ff + ff + j));
+        const float a = kind == 1 ? gelu_tanh_value(g) : g / (1.0f + expf(-g));
+        y[i] = from_f32<T>(a * u);
+    }
+}
+
+extern "C" int ti_gated_act(void* y, const void* gu, int n, int ff, int kind, int dtype, cudaStream_t stream) {
+    if (n == 0) return 0;
+    TI_REQUIRE(ff > 0 && (kind == 0 || kind == 1), "gated_act: size %d, kind %d", ff, kind);
+    const long long count = (long long)n * ff;
+    long long blocks = (count + 255) / 256;
+    if (blocks > ti_sm_count() * 16) blocks = ti_sm_count() * 16;
+    TI_DISPATCH_DTYPE(dtype, (ti_launch(gated_act_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (T*)y, (const T*)gu, ff, kind, (size_t)count)));
+    return ti_check_launch("gated_act");
+}

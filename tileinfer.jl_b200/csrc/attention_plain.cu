@@ -28,7 +28,7 @@ __global__ void attention_plain_kernel(T* __restrict__ out, const T* q, const T*
                                        const T* v_cache, const int* block_table,
                                        int table_stride, const int* tok_slot,
                                        const int* positions, float scale, int nq, int nkv, int D,
-                                       int page_size, int window) {
+                                       int page_size, int window, const float* __restrict__ sink) {
     extern __shared__ float smem[];
     float* qs = smem;                          // [AP_HEADS][D]
     float* sc = smem + AP_HEADS * D;           // [AP_HEADS][AP_CHUNK]
@@ -136,6 +136,8 @@ __global__ void attention_plain_kernel(T* __restrict__ out, const T* q, const T*
 #pragma unroll
     for (int h = 0; h < AP_HEADS; ++h) {
         if (h >= heads) continue;
+        // A sink: one more term exp(sink_h) in the softmax's denominator, with no key and no value.
+        if (sink != nullptr) l[h] += expf(sink[h0 + h] - m[h]);
         T* orow = out + ((size_t)t * nq + h0 + h) * D;
 #pragma unroll
         for (int i = 0; i < ACC; ++i) {
@@ -148,7 +150,7 @@ __global__ void attention_plain_kernel(T* __restrict__ out, const T* q, const T*
 extern "C" int ti_attention_plain(void* out, const void* q, const void* k_cache, const void* v_cache,
                                   const int* block_table, int table_stride, const int* tok_slot, const int* positions,
                                   float scale, int n_tokens, int nq, int nkv, int D, int page_size, int window,
-                                  int dtype, cudaStream_t stream) {
+                                  const float* sink, int dtype, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
     TI_REQUIRE(D > 0 && D <= AP_MAX_D, "attention: head_dim %d exceeds %d", D, AP_MAX_D);
     TI_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads do not divide into %d KV heads", nq, nkv);
@@ -158,6 +160,6 @@ extern "C" int ti_attention_plain(void* out, const void* q, const void* k_cache,
     const size_t smem = (size_t)AP_HEADS * (D + AP_CHUNK) * sizeof(float);
     TI_DISPATCH_DTYPE(dtype, (ti_launch(attention_plain_kernel<T>, dim3(grid), dim3(AP_THREADS), smem, stream, 
                                  (T*)out, (const T*)q, (const T*)k_cache, (const T*)v_cache, block_table, table_stride,
-                                 tok_slot, positions, scale, nq, nkv, D, page_size, window)));
+                                 tok_slot, positions, scale, nq, nkv, D, page_size, window, sink)));
     return ti_check_launch("attention_plain");
 }

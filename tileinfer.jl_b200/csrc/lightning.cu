@@ -1,0 +1,157 @@
+// Linear attention with a decay per head ("lightning" attention): a matrix state per (sequence, head) that is carried
+// from token to token,
+//
+//   S_t = a_h S_(t-1) + k_t v_t^T        S [dim, vdim], 32-bit, zero at the start of a sequence
+//   o_t = S_t^T q_t                      [vdim]
+//
+// with q, k, v = act(projection) (act: SiLU or none; the activation is applied, and rounded to T, as the rows are read).
+//
+//   lightning_scan   the recurrence over the tokens a step brings, from the state the earlier steps left; the new state is
+//                    written back. One kernel serves prompts and one-token steps.
+//   lightning_out    y = T( o / rms(o) * w * sigmoid(g) ): the RMS norm over all heads' outputs together, in 32-bit, times
+//                    the output gate; the input of the output projection.
+//
+// The scan: the columns of S are independent (column j of S sees v_t[j] only), so a block owns 32 columns of one
+// (sequence, head) and walks the sequence's tokens in order; its 8 warps split the rows of S (warp w owns rows w, w + 8,
+// ...), a lane owns one column, the state lives in registers. Tokens are staged 16 at a time in shared memory; the
+// warps' partial sums of o meet there once per 16 tokens. Every sum's order depends on the sizes alone, and a token's
+// result on the sequence's earlier tokens alone, so how a prompt is cut into steps or batched changes no bit.
+// Everything is 32-bit arithmetic; nothing of the state, the decay or o is rounded.
+#include "common.cuh"
+
+#define LS_COLS 32
+#define LS_PARTS 8
+#define LS_TOKENS 16
+#define LS_MAX_DIM 256
+
+__device__ __forceinline__ float silu_value(float z) { return z / (1.0f + expf(-z)); }
+
+template <typename T, int DP>
+__global__ void __launch_bounds__(LS_COLS* LS_PARTS) lightning_scan_kernel(
+    float* __restrict__ o, const T* qkv, long long ld, int q_off, int k_off, int v_off, float* state,
+    const float* __restrict__ decay, const int* cu_seqlens, const int* seq_slots, int H, int D, int V, int act) {
+    extern __shared__ float smem[];
+    float* qs = smem;                                   // [LS_TOKENS][D]
+    float* ks = qs + LS_TOKENS * D;                     // [LS_TOKENS][D]
+    float* vs = ks + LS_TOKENS * D;                     // [LS_TOKENS][LS_COLS]
+    float* part = vs + LS_TOKENS * LS_COLS;             // [LS_TOKENS][LS_PARTS][LS_COLS]
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int col0 = blockIdx.x * LS_COLS, h = blockIdx.y, b = blockIdx.z;
+    const int col = col0 + lane;
+    const float a = decay[h];
+    pdl_enter();
+    const int t0 = __ldcg(cu_seqlens + b), t1 = __ldcg(cu_seqlens + b + 1);
+    const int slot = __ldcg(seq_slots + b);
+    float* S = state + ((size_t)slot * H + h) * D * V;
+    float s[DP];
+#pragma unroll
+    for (int i = 0; i < DP; ++i) {
+        const int d = w + LS_PARTS * i;
+        s[i] = (d < D && col < V) ? __ldcg(S + (size_t)d * V + col) : 0.f;
+    }
+    for (int base = t0; base < t1; base += LS_TOKENS) {
+        const int count = min(LS_TOKENS, t1 - base);
+        __syncthreads();                                // the last round's readers are done
+        for (int e = threadIdx.x; e < count * D; e += blockDim.x) {
+            const int t = e / D, d = e % D;
+            const T* row = qkv + (size_t)(base + t) * ld + (size_t)h * D + d;
+            float qv = to_f32(__ldcg(row + q_off)), kv = to_f32(__ldcg(row + k_off));
+            if (act) { qv = rnd<T>(silu_value(qv)); kv = rnd<T>(silu_value(kv)); }
+            qs[t * D + d] = qv;
+            ks[t * D + d] = kv;
+        }
+        for (int e = threadIdx.x; e < count * LS_COLS; e += blockDim.x) {
+            const int t = e / LS_COLS, c = e % LS_COLS;
+            float vv = 0.f;
+            if (col0 + c < V) {
+                vv = to_f32(__ldcg(qkv + (size_t)(base + t) * ld + v_off + (size_t)h * V + col0 + c));
+                if (act) vv = rnd<T>(silu_value(vv));
+            }
+            vs[t * LS_COLS + c] = vv;
+        }
+        __syncthreads();
+        for (int t = 0; t < count; ++t) {
+            const float vt = vs[t * LS_COLS + lane];
+            const float* qt = qs + t * D;
+            const float* kt = ks + t * D;
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < DP; ++i) {
+                const int d = w + LS_PARTS * i;
+                if (d < D) {
+                    s[i] = fmaf(a, s[i], kt[d] * vt);
+                    acc = fmaf(s[i], qt[d], acc);
+                }
+            }
+            part[(t * LS_PARTS + w) * LS_COLS + lane] = acc;
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < count * LS_COLS; e += blockDim.x) {
+            const int t = e / LS_COLS, c = e % LS_COLS;
+            if (col0 + c >= V) continue;
+            float sum = 0.f;
+#pragma unroll
+            for (int p = 0; p < LS_PARTS; ++p) sum += part[(t * LS_PARTS + p) * LS_COLS + c];
+            o[(size_t)(base + t) * H * V + (size_t)h * V + col0 + c] = sum;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < DP; ++i) {
+        const int d = w + LS_PARTS * i;
+        if (d < D && col < V) S[(size_t)d * V + col] = s[i];
+    }
+}
+
+// o [n, H * V] float; qkv [n, ld] of T with the heads' queries from column q_off on (H * D of them), keys from k_off, values
+// from v_off (H * V); state [slots, H, D, V] float; decay [H] float; cu_seqlens [B + 1], seq_slots [B]. act: 1 = SiLU.
+extern "C" int ti_lightning_scan(float* o, const void* qkv, long long ld, int q_off, int k_off, int v_off, float* state, const float* decay,
+                                 const int* cu_seqlens, const int* seq_slots, int B, int H, int D, int V, int act, int dtype,
+                                 cudaStream_t stream) {
+    if (B == 0) return 0;
+    TI_REQUIRE(H > 0 && D > 0 && V > 0 && D <= LS_MAX_DIM, "lightning_scan: %d heads of %d x %d (the key size is at most %d)", H, D, V, LS_MAX_DIM);
+    TI_REQUIRE(H <= 65535 && B <= 65535, "lightning_scan: %d heads, %d sequences", H, B);
+    const dim3 grid((V + LS_COLS - 1) / LS_COLS, H, B);
+    const size_t smem = (size_t)(2 * LS_TOKENS * D + LS_TOKENS * LS_COLS + LS_TOKENS * LS_PARTS * LS_COLS) * sizeof(float);
+    const int dp = (D + LS_PARTS - 1) / LS_PARTS;
+#define LS_LAUNCH(DP)                                                                                                                \
+    ti_launch(lightning_scan_kernel<T, DP>, grid, dim3(LS_COLS* LS_PARTS), smem, stream, o, (const T*)qkv, ld, q_off, k_off, v_off, state, \
+              decay, cu_seqlens, seq_slots, H, D, V, act)
+    TI_DISPATCH_DTYPE(dtype, {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(lightning_scan_kernel<T, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (dp <= 4) LS_LAUNCH(4);
+        else if (dp <= 8) LS_LAUNCH(8);
+        else if (dp <= 16) LS_LAUNCH(16);
+        else LS_LAUNCH(32);
+    });
+#undef LS_LAUNCH
+    return ti_check_launch("lightning_scan");
+}
+
+template <typename T>
+__global__ void lightning_out_kernel(T* __restrict__ y, const float* o, const T* g, long long ldg, const T* __restrict__ w, float eps, int size) {
+    __shared__ float scratch[33];
+    const float* row = o + (size_t)blockIdx.x * size;
+    float ss = 0.f;
+    pdl_enter();
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+        const float v = __ldcg(row + i);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)size + eps);
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+        float v = __ldcg(row + i) * inv * to_f32(w[i]);
+        if (g != nullptr) v = v / (1.0f + expf(-to_f32(__ldcg(g + (size_t)blockIdx.x * ldg + i))));
+        y[(size_t)blockIdx.x * size + i] = from_f32<T>(v);
+    }
+}
+
+// y [n, size] = T(o / rms(o) * w * sigmoid(g)); o [n, size] float, g [n, ldg] of T (null: no gate), w [size].
+extern "C" int ti_lightning_out(void* y, const float* o, const void* g, long long ldg, const void* w, float eps, int n, int size, int dtype,
+                                cudaStream_t stream) {
+    if (n == 0) return 0;
+    TI_REQUIRE(size > 0, "lightning_out: size %d", size);
+    const int threads = size >= 4096 ? 512 : size >= 1024 ? 256 : 128;
+    TI_DISPATCH_DTYPE(dtype, (ti_launch(lightning_out_kernel<T>, dim3(n), dim3(threads), 0, stream, (T*)y, o, (const T*)g, ldg, (const T*)w, eps, size)));
+    return ti_check_launch("lightning_out");
+}

@@ -2,6 +2,9 @@
 //
 //   router_topk     z = Wr h in 32-bit (one warp per expert and token, lanes stride over the width), score = sigmoid(z);
 //                   the `top` largest (ties to the smaller index) -> ids [n, top], scores [n, top]
+//   router_select   the same choice for routers with more rules: softmax or sigmoid scores, a correction added for the choice only,
+//                   experts in groups of which only the best stay, weights divided by their sum, pass-through choices, a gate
+//                   for the units that every token takes
 //   expert_plan     the (token, choice) pairs grouped by expert: a row for every pair in expert order, every expert's rows
 //                   padded to whole tiles, and the expert of every tile; one block, counts in shared memory
 //   expert_gather   xs[row of the pair] = T(score * h[token]) (the score scales an expert's INPUT) or T(h[token]); padding rows
@@ -82,6 +85,123 @@ extern "C" int ti_router_topk(const void* h, const void* wr, const float* logits
     return ti_check_launch("router_topk");
 }
 
+// A router with more rules. z [n, ldz] holds the 32-bit logits of `total` = experts + pass choices (and, with a gate, one more
+// column: the gate's logit); without z the kernel computes them from h and wr (rows in that order). Per token:
+//   s = softmax(z[0 .. total)) (or sigmoid of each), c = s + correction (the CHOICE score; correction may be null);
+//   the choices form `groups` equal groups of neighbours, a group's score is its largest c, only the `keep` best groups stay
+//   (ties to the smaller index); of those the `top` largest c are chosen (ties to the smaller index);
+//   weight = s of the chosen, divided by (their sum + 1e-20) with `renormalize`.
+// ids [n, top + always]: the chosen expert, or -1 for a pass choice (the last `total - experts`: their output is the input
+// itself), whose weights are summed into pass_weight[n]; then `always` units numbered from `experts` on with the weight
+// sigmoid(gate logit), or 1 without a gate.
+template <typename T>
+__global__ void router_select_kernel(const T* h, const T* __restrict__ wr, const float* z_in, long long ldz, int width, int experts, int total,
+                                     int softmax, const float* __restrict__ correction, int groups, int keep, int top, int renormalize,
+                                     int always, int gate, int* __restrict__ ids, float* __restrict__ scores, float* __restrict__ pass_weight) {
+    __shared__ float z[RT_MAX_EXPERTS + 1], c[RT_MAX_EXPERTS], gs[RT_MAX_EXPERTS];
+    __shared__ float scratch[33];
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int columns = total + (gate ? 1 : 0);
+    pdl_enter();
+    if (z_in != nullptr) {
+        for (int e = threadIdx.x; e < columns; e += RT_THREADS) z[e] = __ldcg(z_in + (size_t)t * ldz + e);
+    } else {
+        const T* row = h + (size_t)t * width;
+        for (int e = warp; e < columns; e += RT_THREADS / 32) {
+            const T* w = wr + (size_t)e * width;
+            float a = 0.f;
+            for (int i = lane; i < width; i += 32) a = fmaf(to_f32(__ldcg(row + i)), to_f32(w[i]), a);
+            a = warp_sum(a);
+            if (lane == 0) z[e] = a;
+        }
+    }
+    __syncthreads();
+    if (softmax) {
+        float m = -INFINITY;
+        for (int e = threadIdx.x; e < total; e += RT_THREADS) m = fmaxf(m, z[e]);
+        m = block_max(m, scratch);
+        float sum = 0.f;
+        for (int e = threadIdx.x; e < total; e += RT_THREADS) sum += expf(z[e] - m);
+        sum = block_sum(sum, scratch);
+        for (int e = threadIdx.x; e < total; e += RT_THREADS) z[e] = expf(z[e] - m) / sum;
+    } else {
+        for (int e = threadIdx.x; e < total; e += RT_THREADS) z[e] = 1.0f / (1.0f + expf(-z[e]));
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < total; e += RT_THREADS) c[e] = z[e] + (correction != nullptr ? correction[e] : 0.f);
+    __syncthreads();
+    const int per = total / groups;
+    if (keep < groups) {
+        for (int g = threadIdx.x; g < groups; g += RT_THREADS) {
+            float best = -INFINITY;
+            for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, c[e]);
+            gs[g] = best;
+        }
+        __syncthreads();
+        // A group stays if fewer than `keep` groups come before it (a larger score, or an equal one with a smaller index).
+        for (int g = threadIdx.x; g < groups; g += RT_THREADS) {
+            int before = 0;
+            for (int o = 0; o < groups; ++o) before += (gs[o] > gs[g] || (gs[o] == gs[g] && o < g)) ? 1 : 0;
+            if (before >= keep)
+                for (int e = g * per; e < (g + 1) * per; ++e) c[e] = -INFINITY;
+        }
+        __syncthreads();
+    }
+    if (warp == 0) {
+        float wsum = 0.f;
+        const size_t out = (size_t)t * (top + always);
+        for (int j = 0; j < top; ++j) {
+            float best = -INFINITY;
+            int arg = 0x7fffffff;
+            for (int e = lane; e < total; e += 32)
+                if (c[e] > best) { best = c[e]; arg = e; }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+                if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+            }
+            if (arg >= total) arg = j;                              // only if nothing comparable is left (NaN)
+            if (lane == 0) {
+                ids[out + j] = arg;
+                scores[out + j] = z[arg];
+                c[arg] = -INFINITY;
+            }
+            wsum += z[arg];
+            __syncwarp();
+        }
+        if (lane == 0) {
+            const float div = renormalize ? wsum + 1e-20f : 1.0f;
+            float pass = 0.f;
+            for (int j = 0; j < top; ++j) {
+                const float wgt = scores[out + j] / div;
+                scores[out + j] = wgt;
+                if (ids[out + j] >= experts) { pass += wgt; ids[out + j] = -1; }
+            }
+            if (pass_weight != nullptr) pass_weight[t] = pass;
+            const float gw = gate ? 1.0f / (1.0f + expf(-z[total])) : 1.0f;
+            for (int a = 0; a < always; ++a) {
+                ids[out + top + a] = experts + a;
+                scores[out + top + a] = gw;
+            }
+        }
+    }
+}
+
+extern "C" int ti_router_select(const void* h, const void* wr, const float* z, long long ldz, int n, int width, int experts, int total, int softmax,
+                                const float* correction, int groups, int keep, int top, int renormalize, int always, int gate, int* ids,
+                                float* scores, float* pass_weight, int dtype, cudaStream_t stream) {
+    if (n == 0) return 0;
+    TI_REQUIRE(experts >= 0 && total >= experts && total >= 1 && total <= RT_MAX_EXPERTS && top >= 1 && top <= total && always >= 0,
+               "router_select: top %d of %d choices (%d experts)", top, total, experts);
+    TI_REQUIRE(groups >= 1 && total % groups == 0 && keep >= 1 && keep <= groups && keep * (total / groups) >= top,
+               "router_select: %d of %d groups over %d choices for top %d", keep, groups, total, top);
+    TI_REQUIRE(total == experts || pass_weight != nullptr, "router_select: pass choices need their weights' output");
+    TI_DISPATCH_DTYPE(dtype, (ti_launch(router_select_kernel<T>, dim3(n), dim3(RT_THREADS), 0, stream, (const T*)h, (const T*)wr, z, ldz, width, experts,
+                                        total, softmax, correction, groups, keep, top, renormalize, always, gate, ids, scores, pass_weight)));
+    return ti_check_launch("router_select");
+}
+
 // The plan of a step: the pairs grouped by expert, every expert's rows padded to whole tiles of `tile` rows, so that a
 // tile holds rows of one expert only (tensor-core kernels then treat a tile like any other; nobody reads the results of
 // padding rows). plan[0] = tiles in use, plan[1 + t] = the expert of tile t. pair_row[pair] = the pair's
@@ -93,7 +213,10 @@ __global__ void expert_plan_kernel(const int* ids, int pairs, int experts, int t
     for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
     for (int r = threadIdx.x; r < capacity; r += blockDim.x) row_pair[r] = -1;
     __syncthreads();
-    for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&count[__ldcg(ids + p)], 1);
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = __ldcg(ids + p);
+        if (e >= 0) atomicAdd(&count[e], 1);             // a negative id: a choice that needs no unit's matrices
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
         int tiles = 0;
@@ -107,6 +230,7 @@ __global__ void expert_plan_kernel(const int* ids, int pairs, int experts, int t
     __syncthreads();
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
         const int e = __ldcg(ids + p);
+        if (e < 0) { pair_row[p] = -1; continue; }
         const int row = first[e] + atomicAdd(&count[e], 1);
         pair_row[p] = row;
         row_pair[row] = p;
@@ -157,6 +281,7 @@ __global__ void expert_gather_kernel(T* __restrict__ xs, const T* h, const int* 
                                      int scale_input) {
     const int p = blockIdx.x;
     pdl_enter();
+    if (__ldcg(pair_row + p) < 0) return;                  // a pair without a row (see expert_plan)
     gather_pair_row(xs, h, __ldcg(pair_row + p), p, scale_input ? __ldcg(scores + p) : 1.0f, per_token, width, (int)threadIdx.x, (int)blockDim.x);
 }
 
@@ -222,25 +347,31 @@ extern "C" int ti_grouped_gemm(void* y, const void* x, const void* w, const int*
 
 template <typename T>
 __global__ void expert_combine_kernel(T* __restrict__ out, const T* y, const int* pair_row, const float* scores, const T* shared,
-                                      int top, int width, int scale_output) {
+                                      const T* h, const float* pass_weight, int top, int width, int scale_output) {
     const int t = blockIdx.x;
     pdl_enter();
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         float a = 0.f;
         for (int j = 0; j < top; ++j) {
             const int p = t * top + j;
-            const float v = to_f32(__ldcg(y + (size_t)__ldcg(pair_row + p) * width + i));
+            const int row = __ldcg(pair_row + p);
+            if (row < 0) continue;                           // a pair without a row: its share comes with pass_weight
+            const float v = to_f32(__ldcg(y + (size_t)row * width + i));
             a += scale_output ? __ldcg(scores + p) * v : v;
         }
         if (shared != nullptr) a += to_f32(__ldcg(shared + (size_t)t * width + i));
+        if (pass_weight != nullptr) a = fmaf(__ldcg(pass_weight + t), to_f32(__ldcg(h + (size_t)t * width + i)), a);
         out[(size_t)t * width + i] = from_f32<T>(a);
     }
 }
 
-extern "C" int ti_expert_combine(void* out, const void* y, const int* pair_row, const float* scores, const void* shared, int n, int top,
-                                 int width, int scale_output, int dtype, cudaStream_t stream) {
+// `pass_weight` [n] with `h` [n, width] (both or neither): pass_weight[t] * h[t] is added, the share of choices that hand their
+// input through unchanged.
+extern "C" int ti_expert_combine(void* out, const void* y, const int* pair_row, const float* scores, const void* shared, const void* h,
+                                 const float* pass_weight, int n, int top, int width, int scale_output, int dtype, cudaStream_t stream) {
     if (n == 0) return 0;
+    TI_REQUIRE((h != nullptr) == (pass_weight != nullptr), "expert_combine: the passed-through share needs both its weights and the input");
     TI_DISPATCH_DTYPE(dtype, (ti_launch(expert_combine_kernel<T>, dim3(n), dim3(width >= 1024 ? 256 : 128), 0, stream, (T*)out, (const T*)y,
-                                        pair_row, scores, (const T*)shared, top, width, scale_output)));
+                                        pair_row, scores, (const T*)shared, (const T*)h, pass_weight, top, width, scale_output)));
     return ti_check_launch("expert_combine");
 }

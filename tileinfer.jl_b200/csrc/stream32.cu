@@ -4,6 +4,7 @@
 //   cast_rows           h = T(x)
 //   norm32              y = T(x / rms(x) * g(w)),  x in 32-bit or in T
 //   branch_norm_add32   x += mult * d / rms(d) * g(w);  then  h = T(x)  or  h = T(x / rms(x) * g_out(w_out))
+//   sum_add_norm32      x += d1 + d2;  then  h = T(x / rms(x) * g_out(w_out))       (two sublayers that read the same input)
 //
 // rms(v) = sqrt(mean(v^2) + eps); g(w) = w, or 1 + w where the checkpoint keeps the gain minus one ("offset"). Everything
 // between the loads and the one rounding on store is 32-bit. d is a sublayer's output: [n, size] in T, or the
@@ -29,13 +30,14 @@ __global__ void embed_positions32_kernel(float* __restrict__ x, const T* __restr
     const T* e = table + (size_t)id * hidden;
     const T* q = pos_table + (size_t)p * hidden;
     float* dst = x + (size_t)t * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32(e[i]) + to_f32(q[i]);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = pos_table != nullptr ? to_f32(e[i]) + to_f32(q[i]) : to_f32(e[i]);
 }
 
 extern "C" int ti_embed_positions32(float* x, const void* table, const void* pos_table, const int* ids, const int* positions,
                                     int n_tokens, int hidden, int vocab, int max_positions, int dtype, int* status,
                                     cudaStream_t stream) {
     if (n_tokens == 0) return 0;
+    if (pos_table == nullptr) max_positions = 1 << 30;          // no position table: the token's row alone
     TI_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0 && max_positions > 0, "embed_positions32: bad sizes n=%d hidden=%d vocab=%d positions=%d",
                n_tokens, hidden, vocab, max_positions);
     const int threads = hidden >= 1024 ? 256 : 128;
@@ -261,4 +263,56 @@ extern "C" int ti_branch_norm_add32(float* x, const void* delta, const float* pa
                   (size_t)partial_stride, gather, per_row, (const T*)w, offset, eps, mult, (T*)h, (const T*)w_out, offset_out, eps_out, size);
     });
     return ti_check_launch("branch_norm_add32");
+}
+
+// Two sublayers read the same normed input and both are added: x += d1 + d2 (d2 may be absent), the sum in 32-bit, then the
+// next reader's input h = T(x / rms(x) * g(w_out)). d1, d2: rows [n, size] of T, or 32-bit partial sums [s, n, size].
+template <typename T>
+__device__ __forceinline__ float branch_value(const T* d, const float* partials, int n_partials, size_t stride, size_t at) {
+    if (partials != nullptr) {
+        float v = __ldcg(partials + at);
+        for (int s = 1; s < n_partials; ++s) v += __ldcg(partials + (size_t)s * stride + at);
+        return v;
+    }
+    return d != nullptr ? to_f32(__ldcg(d + at)) : 0.f;
+}
+
+template <typename T>
+__global__ void sum_add_norm32_kernel(float* x, const T* d1, const float* p1, int n1, size_t s1, const T* d2, const float* p2, int n2, size_t s2,
+                                      T* __restrict__ h, const T* __restrict__ w_out, int offset_out, float eps_out, int size) {
+    extern __shared__ float row_d[];
+    __shared__ float scratch[33];
+    float* row = x + (size_t)blockIdx.x * size;
+    float ss = 0.f;
+    pdl_enter();
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+        const size_t at = (size_t)blockIdx.x * size + i;
+        const float v = __ldcg(row + i) + (branch_value(d1, p1, n1, s1, at) + branch_value(d2, p2, n2, s2, at));
+        row[i] = v;
+        row_d[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (h == nullptr) return;
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)size + eps_out);
+    T* dst = h + (size_t)blockIdx.x * size;
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+        const float g = offset_out ? 1.0f + to_f32(w_out[i]) : to_f32(w_out[i]);
+        dst[i] = from_f32<T>(row_d[i] * inv * g);
+    }
+}
+
+extern "C" int ti_sum_add_norm32(float* x, const void* d1, const float* p1, int n1, long long s1, const void* d2, const float* p2, int n2, long long s2,
+                                 void* h, const void* w_out, int offset_out, float eps_out, int n_rows, int size, int dtype, cudaStream_t stream) {
+    if (n_rows == 0) return 0;
+    TI_REQUIRE(size > 0 && size <= 50000, "sum_add_norm32: size %d", size);
+    TI_REQUIRE((d1 != nullptr) != (p1 != nullptr) && !(d2 != nullptr && p2 != nullptr), "sum_add_norm32: every branch is rows or partial sums");
+    TI_REQUIRE(h == nullptr || w_out != nullptr, "sum_add_norm32: the next input needs its norm's weight");
+    const size_t smem = (size_t)size * sizeof(float);
+    TI_DISPATCH_DTYPE(dtype, {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(sum_add_norm32_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        ti_launch(sum_add_norm32_kernel<T>, dim3(n_rows), dim3(row_threads(size)), smem, stream, x, (const T*)d1, p1, n1, (size_t)s1, (const T*)d2, p2, n2,
+                  (size_t)s2, (T*)h, (const T*)w_out, offset_out, eps_out, size);
+    });
+    return ti_check_launch("sum_add_norm32");
 }

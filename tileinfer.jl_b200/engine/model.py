@@ -26,7 +26,8 @@ def tensor_declarations(spec: ModelSpec) -> List[TensorDecl]:
         decls += lookup("norm", layer.mixer_norm.kind).tensors(layer.mixer_norm)
         decls += lookup("mixer", layer.mixer.kind).tensors(layer.mixer)
         if layer.feed_forward is not None:
-            decls += lookup("norm", layer.feed_forward_norm.kind).tensors(layer.feed_forward_norm)
+            if layer.feed_forward_norm is not None:          # an arrangement with one norm for both sublayers has none
+                decls += lookup("norm", layer.feed_forward_norm.kind).tensors(layer.feed_forward_norm)
             decls += lookup("feed_forward", layer.feed_forward.kind).tensors(layer.feed_forward)
         if layer.token_input is not None:
             decls += lookup("token_input", layer.token_input.kind).tensors(layer.token_input)
@@ -58,7 +59,8 @@ class DecoderModel:
             ffn = n2 = None
             if layer.feed_forward is not None:
                 ffn = lookup("feed_forward", layer.feed_forward.kind)(layer.feed_forward, tensors, rt)
-                n2 = lookup("norm", layer.feed_forward_norm.kind)(layer.feed_forward_norm, tensors, rt)
+                if layer.feed_forward_norm is not None:
+                    n2 = lookup("norm", layer.feed_forward_norm.kind)(layer.feed_forward_norm, tensors, rt)
             n1 = lookup("norm", layer.mixer_norm.kind)(layer.mixer_norm, tensors, rt)
             extra = {}
             if layer.token_input is not None:

@@ -48,7 +48,7 @@ def linear(lin, x, out, epilogue, act, allow_partials=False):
     if n <= GEMV_MAX_TOKENS and k % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
         splits = gemv_splits(lin.out_features, k) if (allow_partials and epilogue == ops.EPI_NONE) else 1
         if splits > 1:
-            partials = lin.rt.buffer("linear.partials", (splits, n, lin.out_features), torch.float32)
+            partials = lin.rt.buffer(lin.partials_name, (splits, n, lin.out_features), torch.float32)
             check(lib().ti_gemv_bf16(partials.data_ptr(), lin.out_features, x.data_ptr(), x.stride(0), w.data_ptr(), n,
                                      lin.out_features, k, splits, 3, 0.0, 0.0, 0.0, 0.0, _stream()), "gemv_bf16")
             return partials
@@ -140,7 +140,7 @@ def _tcgen05_decode(lin, x, out, epilogue, act, allow_partials):
     may_split = allow_partials and epilogue == ops.EPI_NONE
     nt, splits = decode_product_plan(n, lin.out_features, k, 8 if may_split else 1)
     if splits > 1:
-        y = lin.rt.buffer("linear.partials", (splits, n, lin.out_features), torch.float32)
+        y = lin.rt.buffer(lin.partials_name, (splits, n, lin.out_features), torch.float32)
         ldy, epilogue, act = lin.out_features, 3, (0.0, 0.0, 0.0, 0.0)
     else:
         y, ldy = out, out.stride(0)
@@ -163,7 +163,7 @@ def _tcgen05(lin, x, out, epilogue, act, allow_partials):
     st = status_word()
     splits = tc_splits(lin.out_features, k, n) if (allow_partials and epilogue == ops.EPI_NONE) else 1
     if splits > 1:
-        partials = lin.rt.buffer("linear.partials", (splits, n, lin.out_features), torch.float32)
+        partials = lin.rt.buffer(lin.partials_name, (splits, n, lin.out_features), torch.float32)
         rc = lib().ti_gemm_tcgen05(partials.data_ptr(), lin.out_features, x.data_ptr(), x.stride(0), w.data_ptr(), n,
                                    lin.out_features, k, splits, 3, 0.0, 0.0, 0.0, 0.0, st.data_ptr(), _stream())
         if rc == 2:
@@ -295,8 +295,9 @@ SHORT_PROMPT = 384
 SHORT_STEP = 512
 
 
-def attention(out, q, cache, meta, step, spec) -> bool:
-    if q.dtype != torch.bfloat16:
+def attention(out, q, cache, meta, step, spec, sink=None) -> bool:
+    """``sink`` [heads] float32: one more term exp(sink[head]) in every softmax's denominator."""
+    if q.dtype != torch.bfloat16 or sink is not None:
         return False
     if step.is_decode:
         B = step.n_seqs

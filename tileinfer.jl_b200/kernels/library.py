@@ -78,7 +78,7 @@ _SIGNATURES = {
     "ti_add_rmsnorm": [_P, _P, _P, _I, _L, _P, _P, _I, _I, _F, _I, _P],
     "ti_add": [_P, _P, _L, _I, _P],
     "ti_attention_inputs": [_P, _L, _P, _I, _L, _P, _P, _P, _P, _P, _F, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
-    "ti_attention_plain": [_P, _P, _P, _P, _P, _I, _P, _P, _F, _I, _I, _I, _I, _I, _I, _I, _P],
+    "ti_attention_plain": [_P, _P, _P, _P, _P, _I, _P, _P, _F, _I, _I, _I, _I, _I, _I, _P, _I, _P],
     "ti_gemm_plain": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _F, _F, _F, _F, _I, _P],
     "ti_argmax": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
     "ti_sample": [_P, _L, _I, _I, _F, _I, _F, _P, _P, _P, _P, _P],
@@ -174,5 +174,19 @@ _SIGNATURES.update({
     "ti_grouped_gemm": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _F, _F, _I, _P],
     "ti_gemm_tcgen05_grouped": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "ti_gemm_tcgen05_heads": [_P, _P, _P, _I, _I, _I, _I, _P, _P],
-    "ti_expert_combine": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "ti_expert_combine": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+})
+
+# A state carried from token to token (linear attention with decay), projections through a short convolution, two sublayers
+# added at once, routers with more rules, unclamped gated units.
+_SIGNATURES.update({
+    "ti_lightning_scan": [_P, _P, _L, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "ti_lightning_out": [_P, _P, _P, _L, _P, _F, _I, _I, _I, _P],
+    "ti_conv_attention_inputs": [_P, _L, _P, _P, _I, _P, _P, _P, _F, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I,
+                                 _I, _P],
+    "ti_conv_state_update": [_P, _P, _L, _P, _I, _P, _P, _I, _I, _I, _P],
+    "ti_sigmoid_gate": [_P, _P, _P, _L, _I, _I, _I, _I, _I, _P],
+    "ti_sum_add_norm32": [_P, _P, _P, _I, _L, _P, _P, _I, _L, _P, _P, _I, _F, _I, _I, _I, _P],
+    "ti_router_select": [_P, _P, _P, _L, _I, _I, _I, _I, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P],
+    "ti_gated_act": [_P, _P, _I, _I, _I, _I, _P],
 })

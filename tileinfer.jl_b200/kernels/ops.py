@@ -132,14 +132,17 @@ def attention_inputs(qkv, q_out, k_cache, v_cache, q_norm_w, k_norm_w, eps, rota
 
 
 def attention_plain(out, q, k_cache, v_cache, block_table, tok_slot, positions, scale, nq, nkv, head_dim,
-                    page_size, window=0):
+                    page_size, window=0, sink=None):
+    """``sink`` [nq] float32: one more term exp(sink[head]) in every softmax's denominator (no key, no value)."""
+    if sink is not None:
+        _need(sink, "sink", torch.float32)
     _need(out, "out"); _need(q, "q", out.dtype); _need(k_cache, "k_cache", out.dtype); _need(v_cache, "v_cache", out.dtype)
     _need(block_table, "block_table", torch.int32); _need(tok_slot, "tok_slot", torch.int32)
     _need(positions, "positions", torch.int32)
     check(lib().ti_attention_plain(out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
                                    block_table.data_ptr(), block_table.stride(0), tok_slot.data_ptr(),
                                    positions.data_ptr(), scale, q.shape[0], nq, nkv, head_dim, page_size, window or 0,
-                                   dtype_code(out.dtype), _stream()), "attention_plain")
+                                   _ptr(sink), dtype_code(out.dtype), _stream()), "attention_plain")
 
 
 def gemm_plain(y, x, w, epilogue=EPI_NONE, act=(0.0, 0.0, 0.0, 0.0)):
@@ -197,14 +200,17 @@ ACT_GELU_ERF, ACT_GELU_TANH = 0, 1
 
 
 def embed_positions32(x, table, pos_table, ids, positions, status):
-    """x[t] = table[ids[t]] + pos_table[positions[t]], summed and kept in 32-bit."""
-    _need(x, "x", torch.float32); _need(table, "table"); _need(pos_table, "pos_table", table.dtype)
+    """x[t] = table[ids[t]] + pos_table[positions[t]], summed and kept in 32-bit; without ``pos_table`` the token's row alone."""
+    _need(x, "x", torch.float32); _need(table, "table")
     _need(ids, "ids", torch.int32); _need(positions, "positions", torch.int32); _need(status, "status", torch.int32)
     n, hidden = x.shape
-    if table.shape[1] != hidden or pos_table.shape[1] != hidden:
-        raise KernelError(f"embed_positions32: tables {tuple(table.shape)}, {tuple(pos_table.shape)} for a width of {hidden}")
-    check(lib().ti_embed_positions32(x.data_ptr(), table.data_ptr(), pos_table.data_ptr(), ids.data_ptr(), positions.data_ptr(), n,
-                                     hidden, table.shape[0], pos_table.shape[0], dtype_code(table.dtype), status.data_ptr(), _stream()),
+    if pos_table is not None:
+        _need(pos_table, "pos_table", table.dtype)
+    if table.shape[1] != hidden or (pos_table is not None and pos_table.shape[1] != hidden):
+        raise KernelError(f"embed_positions32: table {tuple(table.shape)} for a width of {hidden}")
+    check(lib().ti_embed_positions32(x.data_ptr(), table.data_ptr(), _ptr(pos_table), ids.data_ptr(), positions.data_ptr(), n,
+                                     hidden, table.shape[0], pos_table.shape[0] if pos_table is not None else 0, dtype_code(table.dtype),
+                                     status.data_ptr(), _stream()),
           "embed_positions32")
 
 
@@ -363,11 +369,128 @@ def grouped_gemm(y, x, w, plan, tile, gated=False, limits=None, slope=0.0, shift
                                 _ptr(limits), slope, shift, dtype_code(y.dtype), _stream()), "grouped_gemm")
 
 
-def expert_combine(out, y, pair_row, scores, shared, top, scale_output=False):
+def expert_combine(out, y, pair_row, scores, shared, top, scale_output=False, h=None, pass_weight=None):
+    """out[t] = sum over the token's pairs of (score x) y[row of the pair] (+ shared[t]) (+ pass_weight[t] * h[t]: the share of
+    choices that hand their input through; their pairs have no row)."""
     _need(out, "out"); _need(y, "y", out.dtype); _need(pair_row, "pair_row", torch.int32); _need(scores, "scores", torch.float32)
     if shared is not None:
         _need(shared, "shared", out.dtype)
+    if pass_weight is not None:
+        _need(pass_weight, "pass_weight", torch.float32); _need(h, "h", out.dtype)
     n, width = out.shape
-    check(lib().ti_expert_combine(out.data_ptr(), y.data_ptr(), pair_row.data_ptr(), scores.data_ptr(), _ptr(shared), n, top, width,
-                                  int(bool(scale_output)), dtype_code(out.dtype), _stream()), "expert_combine")
+    check(lib().ti_expert_combine(out.data_ptr(), y.data_ptr(), pair_row.data_ptr(), scores.data_ptr(), _ptr(shared), _ptr(h), _ptr(pass_weight),
+                                  n, top, width, int(bool(scale_output)), dtype_code(out.dtype), _stream()), "expert_combine")
 
+
+
+# ---------------------------------------------------------------- a state carried from token to token; convolved projections
+def _rows_or_partials(d, dtype, name):
+    """(rows pointer, partials pointer, count, stride) of a sublayer's output: [n, size] of ``dtype`` or 32-bit partial sums [s, n, size]."""
+    if d is None:
+        return (None, None, 0, 0)
+    if d.dim() == 3:
+        _need(d, name, torch.float32)
+        return (None, d.data_ptr(), d.shape[0], d.stride(0))
+    _need(d, name, dtype)
+    return (d.data_ptr(), None, 0, 0)
+
+
+def sum_add_norm32(x, d1, d2, h, w_out, eps_out, offset_out=False):
+    """x += d1 + d2 on a 32-bit stream (``d2`` may be None), then h = x / rms(x) * g(w_out) rounded to h's type (``h`` None: the
+    stream's update alone)."""
+    _need(x, "x", torch.float32)
+    n, size = x.shape
+    dtype = h.dtype if h is not None else (d1.dtype if d1.dim() == 2 else d2.dtype)
+    if h is not None:
+        _need(h, "h"); _need(w_out, "w_out", h.dtype)
+    check(lib().ti_sum_add_norm32(x.data_ptr(), *_rows_or_partials(d1, dtype, "d1"), *_rows_or_partials(d2, dtype, "d2"), _ptr(h), _ptr(w_out),
+                                  int(bool(offset_out)), eps_out, n, size, dtype_code(dtype), _stream()), "sum_add_norm32")
+
+
+def lightning_scan(o, rows, q_off, k_off, v_off, state, decay, cu_seqlens, seq_slots, batch, heads, dim, vdim, act=True):
+    """The recurrence S = a_h S + k v^T, o = S^T q over the step's tokens of every sequence, from and to ``state``
+    [slots, heads, dim, vdim] float32. ``rows`` [n, ld]: the projections' output with queries, keys and values from the given
+    columns on; ``act``: SiLU on them. o [n, heads * vdim] float32."""
+    _need(o, "o", torch.float32); _need(rows, "rows", contiguous=False); _need(state, "state", torch.float32); _need(decay, "decay", torch.float32)
+    _need(cu_seqlens, "cu_seqlens", torch.int32); _need(seq_slots, "seq_slots", torch.int32)
+    if rows.stride(1) != 1 or tuple(state.shape[1:]) != (heads, dim, vdim) or decay.numel() != heads:
+        raise KernelError(f"lightning_scan: rows {tuple(rows.shape)}, state {tuple(state.shape)} for {heads} heads of {dim} x {vdim}")
+    check(lib().ti_lightning_scan(o.data_ptr(), rows.data_ptr(), rows.stride(0), q_off, k_off, v_off, state.data_ptr(), decay.data_ptr(),
+                                  cu_seqlens.data_ptr(), seq_slots.data_ptr(), batch, heads, dim, vdim, int(bool(act)), dtype_code(rows.dtype),
+                                  _stream()), "lightning_scan")
+
+
+def lightning_out(y, o, gate, w, eps):
+    """y = o / rms(o) * w * sigmoid(gate), the norm over the whole row in 32-bit; ``gate`` [n, size] (rows may be strided) or None."""
+    _need(y, "y"); _need(o, "o", torch.float32); _need(w, "w", y.dtype)
+    if gate is not None:
+        _need(gate, "gate", y.dtype, contiguous=False)
+    n, size = y.shape
+    check(lib().ti_lightning_out(y.data_ptr(), o.data_ptr(), _ptr(gate), gate.stride(0) if gate is not None else 0, w.data_ptr(), eps, n, size,
+                                 dtype_code(y.dtype), _stream()), "lightning_out")
+
+
+def conv_attention_inputs(rows, bias, conv, taps, state, q_norm_w, k_norm_w, eps, rotation, q_out, k_cache, v_cache, step, slot_map,
+                          nq, nkv, dim, vdim, padded, page_size, write_kv=True):
+    """The step's projected rows (queries, then keys and values with ``write_kv``) -> bias, causal convolution over time (history
+    from ``state`` [slots, taps - 1, channels] float32), whole-row RMS norms of q and k, rotation -> q_out [n, nq, padded] and the
+    keys and values at ``slot_map`` in the pools. ``step`` gives positions, cu_seqlens, seq_slots, kv_lens."""
+    _need(rows, "rows", q_out.dtype, contiguous=False); _need(q_out, "q_out")
+    cos_sin = rotation.cos_sin if rotation is not None else None
+    rotary = int(rotation.rotary_dim) if rotation is not None else 0
+    if rotation is not None and rotation.interleaved:
+        raise KernelError("conv_attention_inputs: only the half-split pairing is built")
+    if state is not None:
+        _need(state, "state", torch.float32)
+    check(lib().ti_conv_attention_inputs(rows.data_ptr(), rows.stride(0), _ptr(bias), _ptr(conv), taps, _ptr(state), _ptr(q_norm_w), _ptr(k_norm_w),
+                                         eps, _ptr(cos_sin), rotary, q_out.data_ptr(), _ptr(k_cache), _ptr(v_cache), step.positions.data_ptr(),
+                                         _ptr(slot_map), step.cu_seqlens.data_ptr(), step.seq_slots.data_ptr(), step.kv_lens.data_ptr(),
+                                         rows.shape[0], step.n_seqs, nq, nkv, dim, vdim, padded, page_size, int(bool(write_kv)),
+                                         dtype_code(q_out.dtype), _stream()), "conv_attention_inputs")
+
+
+def conv_state_update(state, rows, bias, taps, step, channels):
+    """After ``conv_attention_inputs``: every sequence's state becomes its last taps - 1 projected rows."""
+    _need(state, "state", torch.float32); _need(rows, "rows", contiguous=False)
+    check(lib().ti_conv_state_update(state.data_ptr(), rows.data_ptr(), rows.stride(0), _ptr(bias), taps, step.cu_seqlens.data_ptr(),
+                                     step.seq_slots.data_ptr(), step.n_seqs, channels, dtype_code(rows.dtype), _stream()), "conv_state_update")
+
+
+def sigmoid_gate(y, attn, gate, heads, vdim, padded):
+    """y [n, heads * vdim] = attn [n, heads, padded][..., :vdim] * sigmoid(gate [n, heads * vdim]) (``gate`` None: the copy alone)."""
+    _need(y, "y"); _need(attn, "attn", y.dtype)
+    if gate is not None:
+        _need(gate, "gate", y.dtype, contiguous=False)
+    check(lib().ti_sigmoid_gate(y.data_ptr(), attn.data_ptr(), _ptr(gate), gate.stride(0) if gate is not None else 0, y.shape[0], heads, vdim,
+                                padded, dtype_code(y.dtype), _stream()), "sigmoid_gate")
+
+
+def router_select(h, wr, logits, experts, total, top, ids, scores, pass_weight=None, softmax=True, correction=None, groups=1, keep=1,
+                  renormalize=True, always=0, gate=False):
+    """The router with groups, a correction for the choice, normalised weights, pass-through choices and a gated always-on unit
+    (``csrc/routed_experts.cu``: router_select). ``logits`` [n, >= total (+ 1 with gate)] float32 or None (then from h and wr)."""
+    _need(h, "h"); _need(wr, "wr", h.dtype); _need(ids, "ids", torch.int32); _need(scores, "scores", torch.float32)
+    n, width = h.shape
+    if tuple(ids.shape) != (n, top + always) or ids.shape != scores.shape or wr.shape[0] != total + int(bool(gate)):
+        raise KernelError(f"router_select: ids {tuple(ids.shape)}, router {tuple(wr.shape)} for top {top} + {always} of {total}")
+    if logits is not None:
+        _need(logits, "logits", torch.float32, contiguous=False)
+    if correction is not None:
+        _need(correction, "correction", torch.float32)
+    if pass_weight is not None:
+        _need(pass_weight, "pass_weight", torch.float32)
+    check(lib().ti_router_select(h.data_ptr(), wr.data_ptr(), _ptr(logits), logits.stride(0) if logits is not None else 0, n, width, experts, total,
+                                 int(bool(softmax)), _ptr(correction), groups, keep, top, int(bool(renormalize)), always, int(bool(gate)),
+                                 ids.data_ptr(), scores.data_ptr(), _ptr(pass_weight), dtype_code(h.dtype), _stream()), "router_select")
+
+
+ACT_SILU_GATED, ACT_GELU_TANH_GATED = 0, 1
+
+
+def gated_act(y, gu, kind):
+    """y[t, j] = act(gu[t, j]) * gu[t, ff + j]; kind ACT_SILU_GATED or ACT_GELU_TANH_GATED."""
+    _need(y, "y"); _need(gu, "gu", y.dtype)
+    n, ff = y.shape
+    if tuple(gu.shape) != (n, 2 * ff):
+        raise KernelError(f"gated_act: gu {tuple(gu.shape)} for y {tuple(y.shape)}")
+    check(lib().ti_gated_act(y.data_ptr(), gu.data_ptr(), n, ff, kind, dtype_code(y.dtype), _stream()), "gated_act")

@@ -97,7 +97,8 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
-    def cache_request(self) -> Optional[CacheRequest]:
+    def cache_request(self):
+        """What the layer keeps per sequence: a CacheRequest, a tuple of them of different kinds (pages and a state), or None."""
         return None
 
     def decode_plan(self, group) -> Optional[Any]:

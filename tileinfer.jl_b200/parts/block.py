@@ -1,4 +1,5 @@
-"""Arrangement of a layer's parts. ``pre_norm``: x += mixer(norm1(x)); x += ffn(norm2(x)).
+"""Arrangement of a layer's parts. ``pre_norm``: x += mixer(norm1(x)); x += ffn(norm2(x)). ``parallel``: x += mixer(h) + ffn(h),
+h = norm1(x), on a 32-bit stream.
 ``post_norm``: x += m norm1(mixer(x)); x += m norm2(ffn(x)); x += m token_input(x), on a 32-bit stream.
 
 Each residual add is fused with the norm that follows it, so a block receives the already
@@ -61,4 +62,26 @@ class PostNormBlock:
             delta = run()
             last = i + 1 == len(branches)
             norm.branch_add(x, delta, self.mult, h_out if last else h, next_norm if last else self._cast)
+        return h_out
+
+
+@register_block("parallel")
+class ParallelBlock:
+    """One norm, and both sublayers read its output: h = norm1(x); x += mixer(h) + ffn(h) (a layer may have no feed-forward).
+    The stream x is 32-bit; the two outputs are added to it by one kernel that also writes the next reader's normed input. The
+    norms are of a kind that offers ``sum_add`` (``rmsnorm32``)."""
+
+    def __init__(self, spec, mixer, feed_forward, mixer_norm, feed_forward_norm=None):
+        self.spec = spec
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, None
+
+    @property
+    def input_norm(self):
+        return self.mixer_norm
+
+    def forward(self, x, h, step, cache, next_norm, h_out):
+        d1 = self.mixer.forward(h, step, cache)
+        d2 = self.feed_forward.forward(h, step) if self.feed_forward is not None else None
+        next_norm.sum_add(x, d1, d2, h_out)
         return h_out

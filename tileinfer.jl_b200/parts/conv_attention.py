@@ -1,0 +1,133 @@
+"""Grouped-query attention whose projections pass through a short causal convolution over time, with whole-row q/k norms, a
+rotation of part of every head, a sink in the softmax and an output gate.
+
+Per token, from the mixer's input h (every step optional, by the record):
+
+    u = W h + b                      for q [heads, dim], k [kv_heads, dim], v [kv_heads, value_dim]          (``bias``)
+    y_t = sum_j c[:, j] * u_(t - taps + 1 + j)       per channel, zeros before the sequence's start             (``conv_taps``)
+    q, k <- y / rms(y) * w           over the WHOLE row of q, and of k, before the heads are split              (``row_norm``)
+    q, k <- rotation of the first rotary_dim elements of every head (the position encoding's)
+    p_ij = exp(scale * q_i . k_j) / (sum_(j' <= i) exp(scale * q_i . k_j') + exp(sink_head))                    (``sink``)
+    out = Wo ( concat_heads(sum_j p_ij v_j) * sigmoid(Wg h) )                                                   (``gate``)
+
+A sequence keeps its keys (after convolution, norm and rotation) and values (after convolution) in pages, and the last
+taps - 1 rows u as a small fixed-size state: the mixer asks the cache for both. With ``kv_source`` the layer has no key and value
+tensors and reads the pages of an earlier layer, with queries, convolution state and everything else of its own.
+
+Keys and values of different sizes share the paged attention kernels by filling both up to one row length ``padded`` with zeros
+(a zero adds nothing to a score, and the outputs beyond value_dim are dropped by the gate's kernel).
+
+Record: ``num_heads``, ``num_kv_heads``, ``head_dim``, ``scale``, ``window``, ``kv_source``, ``qk_norm_eps`` and the options
+``value_dim``, ``conv_taps`` (0: none), ``bias``, ``row_norm``, ``sink``, ``gate``.
+"""
+from __future__ import annotations
+
+import dataclasses
+
+import torch
+
+from ..config.spec import MixerSpec, TensorDecl
+from ..kernels import ops
+from .base import CacheRequest, Mixer, register_mixer
+from .linear import Linear
+
+
+def _flags(o):
+    return (int(o.get("conv_taps", 0)), bool(o.get("bias", False)), bool(o.get("row_norm", False)), bool(o.get("sink", False)),
+            bool(o.get("gate", False)))
+
+
+@register_mixer("conv_attention")
+class ConvAttention(Mixer):
+    def __init__(self, spec: MixerSpec, tensors, rt, position):
+        self.spec, self.rt = spec, rt
+        o = spec.options
+        self.nq, self.nkv, self.dim, self.vdim = spec.num_heads, spec.num_kv_heads, spec.head_dim, int(o.get("value_dim", spec.head_dim))
+        if self.nkv < 1 or self.nq % self.nkv:
+            raise ValueError(f"conv_attention: {self.nq} query heads do not divide into {self.nkv} KV heads")
+        self.taps, self.bias_on, self.row_norm, self.sink_on, self.gated = _flags(o)
+        self.own_kv = spec.kv_source is None
+        # One row length for keys and values in the pages: the larger of the two sizes, in steps of 16 (what the paged kernels take).
+        self.padded = max(16, -(-max(self.dim, self.vdim) // 16) * 16)
+        if self.padded > ops.MAX_HEAD_DIM:
+            raise ValueError(f"conv_attention: heads of {self.dim} / {self.vdim} exceed the attention kernels' {ops.MAX_HEAD_DIM}")
+        n, p = spec.tensor_names, spec.prefix
+        get = lambda name: rt.param(tensors[p + name])
+        kinds = ["q", "k", "v"] if self.own_kv else ["q"]
+        mats = [get(n[k]) for k in kinds] + ([get(n["g"])] if self.gated else [])
+        self.proj = Linear(torch.cat(mats, 0).contiguous(), rt, "conv_attention_in")
+        self.channels = self.nq * self.dim + (self.nkv * (self.dim + self.vdim) if self.own_kv else 0)
+        self.bias = torch.cat([get(n[k] + n["bias_suffix"]) for k in kinds]).contiguous() if self.bias_on else None
+        self.conv = torch.cat([get(n[k] + n["conv_suffix"]) for k in kinds], 0).contiguous() if self.taps else None
+        self.q_norm = get(n["q"] + n["norm_suffix"]) if self.row_norm else None
+        self.k_norm = get(n["k"] + n["norm_suffix"]) if self.row_norm and self.own_kv else None
+        self.sink = rt.param(tensors[p + n["sink"]], keep_dtype=True).float().contiguous() if self.sink_on else None
+        self.o = Linear(get(n["o"]), rt, "o")
+        self.o.partials_name = "mixer.partials"
+        self.rotation = position.rotation() if position is not None else None
+        # What the paged attention kernels see: heads of the padded size.
+        self.attn_spec = dataclasses.replace(spec, head_dim=self.padded)
+
+    @classmethod
+    def tensors(cls, spec: MixerSpec):
+        n, p, o = spec.tensor_names, spec.prefix, spec.options
+        W, H, G, D = spec.hidden_size, spec.num_heads, spec.num_kv_heads, spec.head_dim
+        V = int(o.get("value_dim", D))
+        taps, bias, row_norm, sink, gate = _flags(o)
+        std = lambda fan_in: ("normal", fan_in ** -0.5)
+        rows = {"q": H * D}
+        if spec.kv_source is None:
+            rows.update({"k": G * D, "v": G * V})
+        out = [TensorDecl(p + n["o"], (W, H * V), std(H * V))]
+        for k, r in rows.items():
+            out.append(TensorDecl(p + n[k], (r, W), std(W)))
+            if bias:
+                out.append(TensorDecl(p + n[k] + n["bias_suffix"], (r,), ("normal", 0.1)))
+            if taps:
+                out.append(TensorDecl(p + n[k] + n["conv_suffix"], (r, taps), ("const_plus_normal", 1.0 / taps, 0.3)))
+            if row_norm and k != "v":
+                out.append(TensorDecl(p + n[k] + n["norm_suffix"], (r,), ("one_plus_normal", 0.1)))
+        if sink:
+            out.append(TensorDecl(p + n["sink"], (H,), ("normal", 1.0), keep_dtype=True))
+        if gate:
+            out.append(TensorDecl(p + n["g"], (H * V, W), std(W)))
+        return out
+
+    def cache_request(self):
+        out = []
+        if self.own_kv:
+            out.append(CacheRequest("paged_kv", kv_heads=self.nkv, head_dim=self.padded, window=self.spec.window))
+        if self.taps > 1:
+            out.append(CacheRequest("state", shape=(self.taps - 1, self.channels), dtype=torch.float32))
+        return tuple(out)
+
+    def decode_plan(self, group):
+        if not (self.rt.fast and self.rt.dtype == torch.bfloat16) or not self.own_kv:
+            return None
+        from ..kernels import fast
+        return fast.SplitKvPlan(self.nkv, group.page_size, group.num_pages * group.page_size)
+
+    def forward(self, h, step, cache):
+        s, rt = self.spec, self.rt
+        n = h.shape[0]
+        nq, nkv, D, V, Dp, C = self.nq, self.nkv, self.dim, self.vdim, self.padded, self.channels
+        rows = rt.buffer("conv_attention.rows", (n, self.proj.out_features))
+        self.proj.forward(h, rows)
+        q = rt.buffer("attention.q", (n, nq, Dp))
+        meta = step.group(cache.group_index)
+        ops.conv_attention_inputs(rows, self.bias, self.conv, self.taps, cache.state, self.q_norm, self.k_norm, s.qk_norm_eps, self.rotation,
+                                  q, cache.k, cache.v, step, meta.slot_mapping, nq, nkv, D, V, Dp, cache.page_size, write_kv=self.own_kv)
+        if self.taps > 1:
+            ops.conv_state_update(cache.state, rows, self.bias, self.taps, step, C)
+        attn = rt.buffer("attention.out", (n, nq * Dp))
+        done = False
+        if rt.fast:
+            from ..kernels import fast
+            done = fast.attention(attn, q, cache, meta, step, self.attn_spec, sink=self.sink)
+        if not done:
+            ops.attention_plain(attn, q, cache.k, cache.v, meta.block_table, step.tok_slot, step.positions, s.scale, nq, nkv, Dp,
+                                cache.page_size, window=s.window or 0, sink=self.sink)
+        y = rt.buffer("conv_attention.gated", (n, nq * V))
+        ops.sigmoid_gate(y, attn, rows[:, C:] if self.gated else None, nq, V, Dp)
+        out = rt.buffer("mixer.delta", (n, s.hidden_size))
+        return self.o.forward(y, out, allow_partials=True)

@@ -62,3 +62,19 @@ class PositionedEmbedding(Embedding):
     def forward_step(self, step, out, status):
         ops.embed_positions32(out, self.table, self.positions, step.token_ids, step.positions, status)
         return out
+
+
+@register_embedding("lookup32")
+class TokenEmbedding32(Embedding):
+    """x = E[token] written to a 32-bit stream (``options["residual_dtype"] == "float32"``), unscaled."""
+
+    def __init__(self, spec: ModelSpec, tensors, rt):
+        self.table = rt.param(tensors[spec.embed_name])
+
+    @classmethod
+    def tensors(cls, spec: ModelSpec):
+        return [TensorDecl(spec.embed_name, (spec.vocab_size, spec.hidden_size), ("normal", spec.options.get("embed_init_std", spec.init_std)))]
+
+    def forward_step(self, step, out, status):
+        ops.embed_positions32(out, self.table, None, step.token_ids, step.positions, status)
+        return out

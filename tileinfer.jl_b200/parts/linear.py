@@ -15,6 +15,8 @@ class Linear:
         self.weight = weight                 # [out, in], compute dtype, on the device
         self.out_features, self.in_features = weight.shape
         self.name = name
+        # Where split-k partial sums go; two products whose partial sums are alive at the same time name different buffers.
+        self.partials_name = "linear.partials"
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, epilogue: int = ops.EPI_NONE, act=(0.0, 0.0, 0.0, 0.0),
                 allow_partials: bool = False):

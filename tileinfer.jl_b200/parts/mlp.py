@@ -86,3 +86,35 @@ class GeluMLP(FeedForward):
         self.up.forward(h, act, self.epilogue)
         out = self.rt.buffer("feed_forward.delta", (n, self.spec.hidden_size))
         return self.down.forward(act, out, allow_partials=True)
+
+
+@register_feed_forward("gated_mlp")
+class GatedMLP(FeedForward):
+    """down(act(gate h) * (up h)), no biases; ``options["activation"]``: "gelu_tanh" or "silu". Gate and up are one product."""
+
+    def __init__(self, spec: FeedForwardSpec, tensors, rt):
+        self.spec, self.rt = spec, rt
+        n, p = spec.tensor_names, spec.prefix
+        self.gate_up = Linear(torch.cat([rt.param(tensors[p + n["gate"]]), rt.param(tensors[p + n["up"]])], 0).contiguous(), rt, "gate_up")
+        self.down = Linear(rt.param(tensors[p + n["down"]]), rt, "down")
+        kinds = {"silu": ops.ACT_SILU_GATED, "gelu_tanh": ops.ACT_GELU_TANH_GATED}
+        act = spec.options.get("activation", "silu")
+        if act not in kinds:
+            raise ValueError(f"gated_mlp: activation {act!r} (known: {', '.join(kinds)})")
+        self.kind = kinds[act]
+
+    @classmethod
+    def tensors(cls, spec: FeedForwardSpec):
+        n, p = spec.tensor_names, spec.prefix
+        W, F = spec.hidden_size, spec.intermediate_size
+        return [TensorDecl(p + n["gate"], (F, W), ("normal", W ** -0.5)), TensorDecl(p + n["up"], (F, W), ("normal", W ** -0.5)),
+                TensorDecl(p + n["down"], (W, F), ("normal", F ** -0.5))]
+
+    def forward(self, h, step):
+        n, F = h.shape[0], self.spec.intermediate_size
+        gu = self.rt.buffer("feed_forward.gate_up", (n, 2 * F))
+        self.gate_up.forward(h, gu)
+        act = self.rt.buffer("feed_forward.act", (n, F))
+        ops.gated_act(act, gu, self.kind)
+        out = self.rt.buffer("feed_forward.delta", (n, self.spec.hidden_size))
+        return self.down.forward(act, out, allow_partials=True)

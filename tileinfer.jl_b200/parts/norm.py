@@ -61,6 +61,11 @@ class RMSNorm32(Norm):
         ops.norm32(out, x, self.weight, self.eps, self.offset)
         return out
 
+    def sum_add(self, x, d1, d2, out):
+        """x += d1 + d2 on a 32-bit stream (two sublayers that read the same input; ``d2`` may be None), then out = norm(x)."""
+        ops.sum_add_norm32(x, d1, d2, out, self.weight, self.eps, self.offset)
+        return out
+
     def branch_add(self, x, delta, mult, h=None, next_norm=None):
         out_norm = next_norm.out_args() if next_norm is not None else None
         if isinstance(delta, GatheredRows):

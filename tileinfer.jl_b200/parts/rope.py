@@ -9,7 +9,8 @@ element type; both elements of a pair share the angle.
 
 Two options of the record go beyond what Apertus uses: ``rotary_dim`` (rotate only the first so
 many elements of a head; default: all) and ``pairing`` ("half": element i with i + rotary_dim/2,
-the default; "interleaved": 2i with 2i + 1).
+the default; "interleaved": 2i with 2i + 1). ``table_dtype`` "float32" keeps cos and sin unrounded in a bfloat16 model, and
+``angles`` "float64" computes frequencies and angles in 64-bit, for mixers that rotate in 32-bit.
 """
 from __future__ import annotations
 
@@ -62,7 +63,11 @@ class RotaryEmbedding(PositionEncoding):
             ang = torch.arange(p0, p1, dtype=torch.float32)[:, None] * inv[None, :]
             table[p0:p1, :, 0] = ang.double().cos().float()
             table[p0:p1, :, 1] = ang.double().sin().float()
-        if rt.dtype != torch.float32:
+        if spec.options.get("angles") == "float64":          # frequencies and angles in 64-bit, one rounding of cos and sin
+            f = float(spec.theta) ** (-torch.arange(0, self.rotary_dim, 2, dtype=torch.float64) / self.rotary_dim)
+            ang = torch.arange(self.max_positions, dtype=torch.float64)[:, None] * f[None, :]
+            table[:, :, 0], table[:, :, 1] = ang.cos().float(), ang.sin().float()
+        if rt.dtype != torch.float32 and spec.options.get("table_dtype") != "float32":
             table = table.to(rt.dtype).float()
         self.cos_sin = table.contiguous().to(rt.device)
 
