@@ -94,25 +94,34 @@ def rotate(x, positions, dims, base):
     return torch.cat([u * cos - v * sin, v * cos + u * sin, x[..., dims:]], -1)
 
 
+def projected(h, W, name, mix, dtype):
+    """W h + b through the convolution, where the layer has one."""
+    u = linear(h, W[name], dtype, W[name + ".b"])
+    return rnd(causal_conv(u, W[name + ".conv"]), dtype) if mix.get("conv") else u
+
+
+def rotated(x, mix):
+    rot = mix.get("rot")
+    return rotate(x, torch.arange(x.shape[0]), rot["dims"], rot["base"]) if rot else x
+
+
 def attention_keys_values(h, W, p, mix, eps, dtype):
     """What a layer with projections of its own keeps of a sequence: keys after convolution, norm and rotation, values
     after convolution. [n, kv_heads, dim], [n, kv_heads, vdim]."""
     n = h.shape[0]
     G, D, V = mix["kv_heads"], mix["dim"], mix["vdim"]
-    k = rnd(causal_conv(linear(h, W[p + "k"], dtype, W[p + "k.b"]), W[p + "k.conv"]), dtype)
-    v = rnd(causal_conv(linear(h, W[p + "v"], dtype, W[p + "v.b"]), W[p + "v.conv"]), dtype)
+    k = projected(h, W, p + "k", mix, dtype)
+    v = projected(h, W, p + "v", mix, dtype)
     k = rms_norm(k, W[p + "k.norm"], eps).view(n, G, D)
-    k = rnd(rotate(k, torch.arange(n), mix["rot"]["dims"], mix["rot"]["base"]), dtype)
-    return k, v.view(n, G, V)
+    return rnd(rotated(k, mix), dtype), v.view(n, G, V)
 
 
 def attention(h, W, p, mix, eps, dtype, keys_values):
     """keys_values: (k, v) of this layer or of the layer that ``kv_from`` names."""
     n = h.shape[0]
     H, G, D, V = mix["heads"], mix["kv_heads"], mix["dim"], mix["vdim"]
-    q = rnd(causal_conv(linear(h, W[p + "q"], dtype, W[p + "q.b"]), W[p + "q.conv"]), dtype)
-    q = rms_norm(q, W[p + "q.norm"], eps).view(n, H, D)
-    q = rnd(rotate(q, torch.arange(n), mix["rot"]["dims"], mix["rot"]["base"]), dtype)
+    q = rms_norm(projected(h, W, p + "q", mix, dtype), W[p + "q.norm"], eps).view(n, H, D)
+    q = rnd(rotated(q, mix), dtype)
     k, v = keys_values
     rep = H // G
     k = k.repeat_interleave(rep, 1)

@@ -39,7 +39,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(
     bf16* __restrict__ out, const bf16* q, const bf16* k_cache, const bf16* v_cache,
     const int* block_table, int table_stride, const int* seq_slots,
     const int* kv_lens, const int* work, float* __restrict__ ws_o, float* __restrict__ ws_ml, float scale_log2e, int nq,
-    int nkv, int splits, int window) {
+    int nkv, int splits, int window, const float* __restrict__ sink) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     typedef DecodeSmem<D> SM;
     constexpr int KS = D / 16, NT = D / 8;
@@ -164,6 +164,8 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(
             O += src[d] * f;
         }
         const int head = kvh * full_group + slab * 16 + row;
+        // A sink: exp(sink[head]) more in the denominator (no key, no value). With several parts the merge adds it.
+        if (splits == 1 && sink != nullptr && L > 0.f) L += exp2f(sink[head] * 1.4426950408889634f - base);
         if (splits == 1) {
             out[((size_t)b * nq + head) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);   // a sequence without keys: zeros
         } else {
@@ -175,7 +177,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(
 }
 
 __global__ void attention_combine_kernel(bf16* __restrict__ out, const float* ws_o,
-                                         const float* ws_ml, const int* seq_work, int D, int nq, int splits) {
+                                         const float* ws_ml, const int* seq_work, int D, int nq, int splits, const float* __restrict__ sink) {
     const size_t row = blockIdx.x;                          // (sequence, head)
     __shared__ float sm[AD_MAX_SPLITS], sl[AD_MAX_SPLITS], sw[AD_MAX_SPLITS];
     __shared__ float s_inv;
@@ -211,6 +213,7 @@ __global__ void attention_combine_kernel(bf16* __restrict__ out, const float* ws
             sw[s] = M == -INFINITY ? 0.f : exp2f(sm[s] - M);     // no part saw a key (a sequence of length 0): zeros, not 0/0
             L += sl[s] * sw[s];
         }
+        if (sink != nullptr && L > 0.f) L += exp2f(sink[row % nq] * 1.4426950408889634f - M);
         s_inv = L > 0.f ? 1.0f / L : 0.f;
     }
     __syncthreads();
@@ -235,7 +238,7 @@ __global__ void attention_combine_kernel(bf16* __restrict__ out, const float* ws
 template <int D>
 static int launch_decode(bf16* out, const bf16* q, const bf16* k, const bf16* v, const int* table, int table_stride,
                          const int* seq_slots, const int* kv_lens, const int* work, const int* seq_work, float* ws_o, float* ws_ml,
-                         float scale, int B, int nq, int nkv, int splits, int window, cudaStream_t stream) {
+                         float scale, int B, int nq, int nkv, int splits, int window, const float* sink, cudaStream_t stream) {
     static bool configured = false;
     const size_t smem = DecodeSmem<D>::BYTES > (size_t)AD_WARPS * 16 * (D + 2) * 4 ? DecodeSmem<D>::BYTES
                                                                                     : (size_t)AD_WARPS * 16 * (D + 2) * 4;
@@ -248,13 +251,13 @@ static int launch_decode(bf16* out, const bf16* q, const bf16* k, const bf16* v,
     const int slabs = (nq / nkv + 15) / 16;
     if (work != nullptr && splits > 1)
         ti_launch(attention_decode_kernel<D, true>, dim3(B * splits, nkv * slabs), dim3(AD_THREADS), smem, stream, out, q, k, v, table, table_stride,
-                  seq_slots, kv_lens, work, ws_o, ws_ml, scale * 1.4426950408889634f, nq, nkv, splits, window);
+                  seq_slots, kv_lens, work, ws_o, ws_ml, scale * 1.4426950408889634f, nq, nkv, splits, window, sink);
     else
         ti_launch(attention_decode_kernel<D, false>, dim3(splits, nkv * slabs, B), dim3(AD_THREADS), smem, stream, out, q, k, v, table, table_stride,
-                  seq_slots, kv_lens, work, ws_o, ws_ml, scale * 1.4426950408889634f, nq, nkv, splits, window);
+                  seq_slots, kv_lens, work, ws_o, ws_ml, scale * 1.4426950408889634f, nq, nkv, splits, window, sink);
     if (int rc = ti_check_launch("attention_decode")) return rc;
     if (splits > 1) {
-        ti_launch(attention_combine_kernel, dim3(B * nq), dim3(D <= 64 ? 64 : 128), 0, stream, out, ws_o, ws_ml, seq_work, D, nq, splits);
+        ti_launch(attention_combine_kernel, dim3(B * nq), dim3(D <= 64 ? 64 : 128), 0, stream, out, ws_o, ws_ml, seq_work, D, nq, splits, sink);
         return ti_check_launch("attention_combine");
     }
     return 0;
@@ -266,10 +269,11 @@ static int launch_decode(bf16* out, const bf16* q, const bf16* k, const bf16* v,
 // the sequences, so that long sequences get more parts than short ones. work[slot] = (sequence << 16 |
 // part << 8 | parts (at most 32), or -1 for a slot left without work; the sequence's length), 8-byte aligned
 // pairs; seq_work[sequence] = first slot << 8 | parts; a sequence's slots are consecutive. Without them every sequence takes `splits` equal parts.
-extern "C" int ti_attention_decode_shared(void* out, const void* q, const void* k_cache, const void* v_cache,
-                                          const int* block_table, int table_stride, const int* seq_slots, const int* kv_lens,
-                                          const int* work, const int* seq_work, float* ws_o, float* ws_ml, float scale, int B,
-                                          int nq, int nkv, int D, int page_size, int splits, int window, cudaStream_t stream) {
+// `sink` [nq] float (or null): one more term exp(sink[head]) in every softmax's denominator, with no key and no value.
+extern "C" int ti_attention_decode_sink(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                        const int* block_table, int table_stride, const int* seq_slots, const int* kv_lens,
+                                        const int* work, const int* seq_work, float* ws_o, float* ws_ml, float scale, int B,
+                                        int nq, int nkv, int D, int page_size, int splits, int window, const float* sink, cudaStream_t stream) {
     if (B == 0) return 0;
     if (page_size != AD_PAGE || nq % nkv != 0 || nq / nkv > 128 || D % 16 != 0 || B > 32767 || (long long)nkv * ((nq / nkv + 15) / 16) > 65535) {
         ti_fail("attention_decode takes page size %d, at most 128 query heads per KV head and head sizes in steps of 16; "
@@ -283,7 +287,7 @@ extern "C" int ti_attention_decode_shared(void* out, const void* q, const void* 
 #define AD_CASE(d)                                                                                                     \
     case d:                                                                                                            \
         return launch_decode<d>((bf16*)out, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, block_table,     \
-                                table_stride, seq_slots, kv_lens, work, seq_work, ws_o, ws_ml, scale, B, nq, nkv, splits, window, stream);
+                                table_stride, seq_slots, kv_lens, work, seq_work, ws_o, ws_ml, scale, B, nq, nkv, splits, window, sink, stream);
     switch (D) {
         AD_CASE(16) AD_CASE(32) AD_CASE(48) AD_CASE(64) AD_CASE(80) AD_CASE(96) AD_CASE(112) AD_CASE(128) AD_CASE(256)
         default:
@@ -291,6 +295,14 @@ extern "C" int ti_attention_decode_shared(void* out, const void* q, const void* 
             return 2;
     }
 #undef AD_CASE
+}
+
+extern "C" int ti_attention_decode_shared(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                          const int* block_table, int table_stride, const int* seq_slots, const int* kv_lens,
+                                          const int* work, const int* seq_work, float* ws_o, float* ws_ml, float scale, int B,
+                                          int nq, int nkv, int D, int page_size, int splits, int window, cudaStream_t stream) {
+    return ti_attention_decode_sink(out, q, k_cache, v_cache, block_table, table_stride, seq_slots, kv_lens, work, seq_work, ws_o, ws_ml, scale,
+                                    B, nq, nkv, D, page_size, splits, window, nullptr, stream);
 }
 
 // Returns 2 (and sets the error text) when the sizes are outside what this kernel takes, so

@@ -47,7 +47,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attention_prefill_kernel(
     bf16* __restrict__ out, const bf16* q, const bf16* k_cache, const bf16* v_cache,
     const int* block_table, int table_stride, const int* seq_slots,
     const int* cu_seqlens, const int* kv_lens, int n_seqs, float scale_log2e, int nq, int nkv,
-    int tokens_per_tile, int window) {
+    int tokens_per_tile, int window, const float* __restrict__ sink) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     typedef PrefillSmem<D> SM;
     constexpr int CPR = D / 8, KS = D / 16, NT = D / 8;
@@ -203,6 +203,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attention_prefill_kernel(
     cp_async_wait<0>();
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if (sink != nullptr) {                   // exp(sink[head]) more in the denominator: no key, no value
+        if (live0) l0 += exp2f(sink[kvh * group + r0 % group] * 1.4426950408889634f - m0);
+        if (live1) l1 += exp2f(sink[kvh * group + r1 % group] * 1.4426950408889634f - m1);
+    }
     const float i0 = live0 ? 1.0f / l0 : 0.f, i1 = live1 ? 1.0f / l1 : 0.f;
     bf16* oa = out + ((size_t)(q_begin + j0 + (live0 ? tok0 : 0)) * nq + (size_t)kvh * group + r0 % group) * D;
     bf16* ob = out + ((size_t)(q_begin + j0 + (live1 ? tok1 : 0)) * nq + (size_t)kvh * group + r1 % group) * D;
@@ -217,7 +221,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attention_prefill_kernel(
 template <int D>
 static int launch_prefill(bf16* out, const bf16* q, const bf16* k, const bf16* v, const int* table, int table_stride,
                           const int* seq_slots, const int* cu_seqlens, const int* kv_lens, int n_seqs, int total_tiles,
-                          float scale, int nq, int nkv, int tokens_per_tile, int window, cudaStream_t stream) {
+                          float scale, int nq, int nkv, int tokens_per_tile, int window, const float* sink, cudaStream_t stream) {
     static bool configured = false;
     const size_t smem = PrefillSmem<D>::BYTES;
     if (!configured) {
@@ -228,17 +232,18 @@ static int launch_prefill(bf16* out, const bf16* q, const bf16* k, const bf16* v
     dim3 grid(total_tiles, nkv);
     ti_launch(attention_prefill_kernel<D>, dim3(grid), dim3(PF_THREADS), smem, stream, out, q, k, v, table, table_stride, seq_slots, cu_seqlens,
                                                                    kv_lens, n_seqs, scale * 1.4426950408889634f, nq, nkv,
-                                                                   tokens_per_tile, window);
+                                                                   tokens_per_tile, window, sink);
     return ti_check_launch("attention_prefill");
 }
 
 // `total_tiles` = sum over the sequences of ceil(tokens of the sequence / tokens_per_tile), with
 // tokens_per_tile = 128 / (query heads per KV head). Returns 2 when the sizes are outside what the
 // kernel takes (the caller then runs the plain kernel).
-extern "C" int ti_attention_prefill(void* out, const void* q, const void* k_cache, const void* v_cache,
-                                    const int* block_table, int table_stride, const int* seq_slots,
-                                    const int* cu_seqlens, const int* kv_lens, int n_seqs, int total_tiles, float scale,
-                                    int nq, int nkv, int D, int page_size, int window, cudaStream_t stream) {
+// `sink` [nq] float (or null): one more term exp(sink[head]) in every softmax's denominator.
+extern "C" int ti_attention_prefill_sink(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                         const int* block_table, int table_stride, const int* seq_slots,
+                                         const int* cu_seqlens, const int* kv_lens, int n_seqs, int total_tiles, float scale,
+                                         int nq, int nkv, int D, int page_size, int window, const float* sink, cudaStream_t stream) {
     if (n_seqs == 0 || total_tiles == 0) return 0;
     if (page_size != PF_PAGE || nq % nkv != 0 || nq / nkv > PF_ROWS || D % 16 != 0 || nkv > 65535) {
         ti_fail("attention_prefill takes page size %d, at most %d query heads per KV head and head sizes in steps of 16; "
@@ -250,7 +255,7 @@ extern "C" int ti_attention_prefill(void* out, const void* q, const void* k_cach
     case d:                                                                                                            \
         return launch_prefill<d>((bf16*)out, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, block_table,    \
                                  table_stride, seq_slots, cu_seqlens, kv_lens, n_seqs, total_tiles, scale, nq, nkv,    \
-                                 tokens_per_tile, window, stream);
+                                 tokens_per_tile, window, sink, stream);
     switch (D) {
         PF_CASE(16) PF_CASE(32) PF_CASE(48) PF_CASE(64) PF_CASE(80) PF_CASE(96) PF_CASE(112) PF_CASE(128) PF_CASE(256)
         default:
@@ -258,4 +263,12 @@ extern "C" int ti_attention_prefill(void* out, const void* q, const void* k_cach
             return 2;
     }
 #undef PF_CASE
+}
+
+extern "C" int ti_attention_prefill(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                    const int* block_table, int table_stride, const int* seq_slots,
+                                    const int* cu_seqlens, const int* kv_lens, int n_seqs, int total_tiles, float scale,
+                                    int nq, int nkv, int D, int page_size, int window, cudaStream_t stream) {
+    return ti_attention_prefill_sink(out, q, k_cache, v_cache, block_table, table_stride, seq_slots, cu_seqlens, kv_lens, n_seqs, total_tiles,
+                                     scale, nq, nkv, D, page_size, window, nullptr, stream);
 }

@@ -40,6 +40,7 @@ struct Params {
     int n_seqs, heads, kv_heads, group, window;
     float scale_log2;
     int* status;
+    const float* sink;         // [heads] or null: exp(sink[head]) more in every softmax's denominator
 };
 
 template <int D> struct Cfg {
@@ -331,6 +332,8 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
             tc_fence_after();
         }
         if (ok) {
+            // l sums exp2(score - m_used); the sink's term is taken against the same reference.
+            if (p.sink != nullptr && l > 0.f && head < p.heads) l += exp2f(p.sink[head] * 1.4426950408889634f - m_used);
             const float inv = l > 0.f ? 1.f / l : 0.f;
             bf16* dst = p.out + ((size_t)(tok_begin + tok) * p.heads + head) * D;
 #pragma unroll 1
@@ -383,11 +386,11 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
 // non-zero value afterwards means a wait ran out. Returns 2 when the sizes are outside what this kernel
 // takes (head size 64 or 128, 1 to 128 query heads per KV head, pages of 64): the caller then runs the
 // kernel for all sizes.
-extern "C" int ti_attention_prefill_tc(void* out, const void* q, const void* k_cache, const void* v_cache, int n_pages,
-                                       const int* block_table, int table_stride, const int* seq_slots,
-                                       const int* cu_seqlens, const int* kv_lens, int n_seqs, int n_tokens, int total_blocks,
-                                       float scale, int nq, int nkv, int D, int page_size, int window, int* status,
-                                       cudaStream_t stream) {
+extern "C" int ti_attention_prefill_tc_sink(void* out, const void* q, const void* k_cache, const void* v_cache, int n_pages,
+                                            const int* block_table, int table_stride, const int* seq_slots,
+                                            const int* cu_seqlens, const int* kv_lens, int n_seqs, int n_tokens, int total_blocks,
+                                            float scale, int nq, int nkv, int D, int page_size, int window, int* status,
+                                            const float* sink, cudaStream_t stream) {
     if (n_seqs == 0 || total_blocks == 0) return 0;
     const int group = nkv > 0 ? nq / nkv : 0;
     if (page_size != PAGE || nkv <= 0 || nq % nkv != 0 || group < 1 || group > ROWS || (D != 64 && D != 128) || nkv > 65535 ||
@@ -400,7 +403,7 @@ extern "C" int ti_attention_prefill_tc(void* out, const void* q, const void* k_c
     Params p;
     p.out = (bf16*)out; p.table = block_table; p.table_stride = table_stride; p.slots = seq_slots; p.cu_seqlens = cu_seqlens;
     p.kv_lens = kv_lens; p.n_seqs = n_seqs; p.heads = nq; p.kv_heads = nkv; p.group = group; p.window = window;
-    p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+    p.scale_log2 = scale * 1.4426950408889634f; p.status = status; p.sink = sink;
     CUtensorMap mq, mk, mv;
     {
         const unsigned long long dims[3] = {(unsigned long long)D, (unsigned long long)nq, (unsigned long long)n_tokens};
@@ -417,4 +420,13 @@ extern "C" int ti_attention_prefill_tc(void* out, const void* q, const void* k_c
     }
     return D == 64 ? launch<64>(mq, mk, mv, (const bf16*)q, p, total_blocks, stream)
                    : launch<128>(mq, mk, mv, (const bf16*)q, p, total_blocks, stream);
+}
+
+extern "C" int ti_attention_prefill_tc(void* out, const void* q, const void* k_cache, const void* v_cache, int n_pages,
+                                       const int* block_table, int table_stride, const int* seq_slots,
+                                       const int* cu_seqlens, const int* kv_lens, int n_seqs, int n_tokens, int total_blocks,
+                                       float scale, int nq, int nkv, int D, int page_size, int window, int* status,
+                                       cudaStream_t stream) {
+    return ti_attention_prefill_tc_sink(out, q, k_cache, v_cache, n_pages, block_table, table_stride, seq_slots, cu_seqlens, kv_lens, n_seqs,
+                                        n_tokens, total_blocks, scale, nq, nkv, D, page_size, window, status, nullptr, stream);
 }

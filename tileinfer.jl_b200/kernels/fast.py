@@ -297,8 +297,13 @@ SHORT_STEP = 512
 
 def attention(out, q, cache, meta, step, spec, sink=None) -> bool:
     """``sink`` [heads] float32: one more term exp(sink[head]) in every softmax's denominator."""
-    if q.dtype != torch.bfloat16 or sink is not None:
+    if q.dtype != torch.bfloat16:
         return False
+    # The entry points with a sink take it as one more argument before the stream; without a sink the plain ones are called.
+    extra = (sink.data_ptr(),) if sink is not None else ()
+    L = lib()
+    decode_fn, tc_fn, mma_fn = ((L.ti_attention_decode_sink, L.ti_attention_prefill_tc_sink, L.ti_attention_prefill_sink) if sink is not None
+                                else (L.ti_attention_decode_shared, L.ti_attention_prefill_tc, L.ti_attention_prefill))
     if step.is_decode:
         B = step.n_seqs
         # The step's plan carries the split count and how the work slots are shared out among the sequences.
@@ -309,13 +314,13 @@ def attention(out, q, cache, meta, step, spec, sink=None) -> bool:
         rt_buffer = step.runtime.buffer
         ws_o = rt_buffer("attention.ws_o", (B * splits, spec.num_heads, spec.head_dim), torch.float32)
         ws_ml = rt_buffer("attention.ws_ml", (B * splits, spec.num_heads, 2), torch.float32)
-        rc = lib().ti_attention_decode_shared(out.data_ptr(), q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
+        rc = decode_fn(out.data_ptr(), q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
                                               meta.block_table.data_ptr(), meta.block_table.stride(0),
                                               step.seq_slots.data_ptr(), step.kv_lens.data_ptr(),
                                               work.data_ptr() if shared else None,
                                               seq.data_ptr() if shared else None, ws_o.data_ptr(),
                                               ws_ml.data_ptr(), spec.scale, B, spec.num_heads, spec.num_kv_heads,
-                                              spec.head_dim, cache.page_size, splits, spec.window or 0, _stream())
+                                              spec.head_dim, cache.page_size, splits, spec.window or 0, *extra, _stream())
         if rc == 2:
             return False
         check(rc, "attention_decode")
@@ -333,20 +338,20 @@ def attention(out, q, cache, meta, step, spec, sink=None) -> bool:
     # set-up outweighs its products (a layer of one 256-token prompt: 12 us less; level at 448 tokens; the tensor-memory
     # kernel 2 us ahead at 512, and ahead for four or more prompts of 256 tokens in one step).
     short = step.max_kv_len <= SHORT_PROMPT and step.n_tokens <= SHORT_STEP
-    rc = 2 if short else lib().ti_attention_prefill_tc(out.data_ptr(), q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), cache.k.shape[0],
+    rc = 2 if short else tc_fn(out.data_ptr(), q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), cache.k.shape[0],
                                        meta.block_table.data_ptr(), meta.block_table.stride(0), step.seq_slots.data_ptr(),
                                        step.cu_seqlens.data_ptr(), step.kv_lens.data_ptr(), step.n_seqs, step.n_tokens, blocks,
                                        spec.scale, spec.num_heads, spec.num_kv_heads, spec.head_dim, cache.page_size,
-                                       spec.window or 0, status_word().data_ptr(), _stream())
+                                       spec.window or 0, status_word().data_ptr(), *extra, _stream())
     if rc != 2:
         check(rc, "attention_prefill_tc")
         return True
     total_tiles = sum(-(-n // tokens_per_tile) for n in step.host_q_lens)
-    rc = lib().ti_attention_prefill(out.data_ptr(), q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
+    rc = mma_fn(out.data_ptr(), q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
                                     meta.block_table.data_ptr(), meta.block_table.stride(0), step.seq_slots.data_ptr(),
                                     step.cu_seqlens.data_ptr(), step.kv_lens.data_ptr(), step.n_seqs, total_tiles,
                                     spec.scale, spec.num_heads, spec.num_kv_heads, spec.head_dim, cache.page_size,
-                                    spec.window or 0, _stream())
+                                    spec.window or 0, *extra, _stream())
     if rc == 2:
         return False
     check(rc, "attention_prefill")

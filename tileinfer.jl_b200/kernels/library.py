@@ -155,6 +155,10 @@ _SIGNATURES_FAST = {
     "ti_attention_decode_shared": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _I, _P],
     "ti_attention_prefill_tc": [_P, _P, _P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _F, _I, _I, _I, _I, _I, _P, _P],
 }
+# The same kernels with a sink: a last argument [heads] float32 (or null) before the stream.
+_SIGNATURES_FAST["ti_attention_prefill_sink"] = _SIGNATURES_FAST["ti_attention_prefill"][:-1] + [_P, _P]
+_SIGNATURES_FAST["ti_attention_decode_sink"] = _SIGNATURES_FAST["ti_attention_decode_shared"][:-1] + [_P, _P]
+_SIGNATURES_FAST["ti_attention_prefill_tc_sink"] = _SIGNATURES_FAST["ti_attention_prefill_tc"][:-1] + [_P, _P]
 _SIGNATURES.update(_SIGNATURES_FAST)
 
 # The 32-bit residual stream, latent attention's inputs, per-head and per-expert products, activations.
