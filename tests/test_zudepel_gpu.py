@@ -152,7 +152,8 @@ def test_one_far_key_stands_out_among_hundreds_and_the_sink_takes_its_share(dtyp
     from test_parts_gpu import OneStep
     T = DTYPES[dtype]
     W, scale = 16, 1.5
-    for sink, share in ((-30.0, 1.0), (scale * 16.0, 0.5)):
+    marked_score = scale * 4.0 / math.sqrt(1.0625 / 16)              # an ordinary query (4 e0 after the norm) on the marked key
+    for sink, share in ((-30.0, 1.0), (marked_score, 0.5)):
         tensors = _identity_attention_weights(W, 2, sink)
         tensors["m.q"][0, 1] = 1.0; tensors["m.q"][1, 1] = 0.0       # e1 -> e0: ordinary tokens ask along e0 as well
         mixer, spec = _conv_attention(T, W, 1, 1, W, W, scale, 2, None, tensors)
@@ -166,11 +167,11 @@ def test_one_far_key_stands_out_among_hundreds_and_the_sink_takes_its_share(dtyp
             out = [env.run(mixer, [(slot, h[:prompt_len].to(T))], W)]
             out += [env.run(mixer, [(slot, h[t:t + 1].to(T))], W) for t in range(prompt_len, total)]
             out = torch.cat(out)
-            # The marked row after the norm: (1, 0, 0.25, ...) / rms; its e2 element reaches the output times the share.
-            rms = math.sqrt((1.0 + 0.0625) / W)
-            want = 0.25 / rms * share * 0.5                       # the open gate is sigmoid(0)
-            seen = out[mark_at:, 2]
-            assert float((seen - want).abs().max()) <= 0.02 * want, f"sink {sink}, marker at {mark_at}: {seen[:3].tolist()} .. {seen[-3:].tolist()}, want {want}"
+            # Values are not normed: the marker's 0.25 at e2 reaches the output times the share and the half-open gate.
+            want = 0.25 * share * 0.5
+            seen = out[mark_at + 1:, 2]                           # (the marked token's own query is longer: its share differs)
+            assert float((seen - want).abs().max()) <= (0.005 if T == torch.float32 else 0.04) * want, \
+                f"sink {sink}, marker at {mark_at}: {seen[:3].tolist()} .. {seen[-3:].tolist()}, want {want}"
             assert float(out[:mark_at, 2].abs().max()) == 0.0 if mark_at else True
 
 
@@ -377,12 +378,11 @@ def test_every_attention_kernel_counts_the_sink():
         tensors[f"m.{k}.conv"] = R(r, 3, s=0.5)
     tensors["m.q.norm"], tensors["m.k.norm"] = 1 + R(H * D, s=0.1), 1 + R(G * D, s=0.1)
     mix = {"heads": H, "kv_heads": G, "dim": D, "vdim": V, "scale": 0.3, "conv": 3, "rot": {"dims": 32, "base": 1000.0}}
-    for kernels, lens in (("fast", [700]), ("fast", [90, 30]), ("plain", [130])):
+    for kernels, lens in (("fast", [480]), ("fast", [90, 30]), ("plain", [130])):
         mixer, spec = _conv_attention(T, W, H, G, D, V, 0.3, 3, (32, 1000.0), tensors)
         mixer.rt.kernels = kernels
         hs = [R(n + 24, W) for n in lens]
         env = OneStep(mixer, T, max_tokens=2048, max_seqs=2)
-        env.planner.max_step_tokens = 1024
         slots = [env.cache.alloc_slot() for _ in lens]
         library.call_counts.clear()
         out = env.run(mixer, [(s, h[:n].to(T)) for s, h, n in zip(slots, hs, lens)], W)
@@ -392,7 +392,7 @@ def test_every_attention_kernel_counts_the_sink():
         used = dict(library.call_counts)
         if kernels == "fast":
             assert used.get("ti_attention_decode_sink", 0) == 24 and "ti_attention_plain" not in used
-            assert used.get("ti_attention_prefill_tc_sink" if lens[0] > 500 else "ti_attention_prefill_sink", 0) == 1
+            assert used.get("ti_attention_prefill_tc_sink" if lens[0] > 400 else "ti_attention_prefill_sink", 0) == 1
         else:
             assert used.get("ti_attention_plain", 0) == 25
         W64 = {k: v.to(F64) for k, v in tensors.items()}
@@ -400,7 +400,9 @@ def test_every_attention_kernel_counts_the_sink():
             kv = plain.attention_keys_values(h, W64, "m.", mix, 1e-6, T)
             ref = plain.attention(h, W64, "m.", mix, 1e-6, T, kv).float()
             got = torch.cat([o[i] for o in outs])
-            assert float((got - ref).abs().max()) <= 4 * 2.0 ** -8 * float(ref.abs().max()), f"{kernels} {lens} sequence {i}"
+            err = (got - ref).abs().max(-1).values
+            assert float(err.max()) <= 6 * 2.0 ** -8 * float(ref.abs().max()), \
+                f"{kernels} {lens} sequence {i}: worst at {int(err.argmax())}: {float(err.max()):.3g} (scale {float(ref.abs().max()):.3g}); first bad {int((err > 6 * 2.0 ** -8 * float(ref.abs().max())).float().argmax())}"
 
 
 # ---------------------------------------------------------------- through the public entry points
@@ -455,7 +457,7 @@ def test_bfloat16_steps_take_the_fast_kernels(models):
     engine.free_sequence(slot)
     engine.check_health()
     used = library.call_counts
-    assert used.get("ti_gemm_tcgen05_grouped", 0) == 4 and used.get("ti_router_select", 0) == 4
+    assert used.get("ti_gemm_tcgen05_grouped", 0) == 8 and used.get("ti_router_select", 0) == 4
     assert used.get("ti_attention_prefill_tc_sink", 0) == 3 and used.get("ti_attention_decode_sink", 0) == 3
     assert used.get("ti_lightning_scan", 0) == 2 and used.get("ti_conv_attention_inputs", 0) == 6
     assert "ti_grouped_gemm" not in used and "ti_attention_plain" not in used and "ti_gemm_plain" not in used

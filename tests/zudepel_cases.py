@@ -125,9 +125,9 @@ class Model:
         key = (tuple(tokens), dtype)
         if key not in self._refs:
             logits, _, margins = plain.forward(self.cfg, self.W, tokens, dtype, return_layers=True)
-            # A choice score is a softmax value plus a constant; rounding the router's input to bfloat16 moves it by about a
-            # ten-thousandth (seen between this implementation's two precisions), 32-bit arithmetic by a few millionths.
-            unsure = margins < (1e-3 if dtype == torch.bfloat16 else 2e-5)
+            # A choice score is a softmax value plus a constant; rounding the router's input to bfloat16 moves it, with what earlier layers rounded, by up to
+            # five thousandths (choices with such margins were seen to turn), 32-bit arithmetic by a few millionths.
+            unsure = margins < (2e-2 if dtype == torch.bfloat16 else 2e-5)
             self._refs[key] = (logits.float().numpy(), unsure.numpy())
         return self._refs[key]
 
@@ -143,16 +143,16 @@ def tolerance(dtype, ref: np.ndarray) -> float:
     return 1e-4 * scale if dtype == torch.float32 else 8 * scale * 2.0 ** -8
 
 
-def compare(model: Model, tokens, got: dict, dtype, what: str = "", need: float = 0.5):
-    """``got``: position -> logits row. Every position from the start up to the first close router call must be within
-    the tolerance (a turned choice changes its own position and, through states and keys, every later one); at least
-    ``need`` of the positions (of 20 or more) must be of that kind."""
+def compare(model: Model, tokens, got: dict, dtype, what: str = "", need: float = 0.8):
+    """``got``: position -> logits row. Every position whose own router choices are settled must be within the tolerance
+    (a choice that rounding turns changes its own position by an expert's whole share; what later positions see of it
+    through states and keys is one token's part among many, and stays within the tolerance); at least ``need`` of the
+    positions (of 20 or more) must be of that kind."""
     ref, unsure = model.reference(tokens, dtype)
     tol = tolerance(dtype, ref)
-    first = int(np.argmax(unsure)) if unsure.any() else len(tokens)
-    sure = [p for p in got if p < first]
+    sure = [p for p in got if not unsure[p]]
     if len(got) >= 20:
-        assert len(sure) >= need * len(got), f"{what}: only {len(sure)} of {len(got)} positions come before a close router call"
+        assert len(sure) >= need * len(got), f"{what}: only {len(sure)} of {len(got)} positions are free of close router calls"
     for p in sure:
         err = float(np.abs(got[p] - ref[p]).max())
         assert err <= tol, f"{what}: position {p} of {len(tokens)}: |d| = {err:.3g} > {tol:.3g}"
