@@ -5,6 +5,7 @@ model with random weights (bfloat16), plus prefill throughput and roofline fract
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--dtype bfloat16|float32] [--impl reference]
     python bench.py --preset 8b-long | 70b        (the other two sizes the reference names; a line each)
     python bench.py --preset vogilix [--timeline]  (the Vogilix design at two sizes beside Apertus layers of equal size)
+    python bench.py --preset zudepel [--timeline]  (the Zudepel design at two sizes beside Vogilix layers of equal size)
 
 Prints one JSON line. A "step" is one decode step of the whole batch (default batch 8, every
 sequence after 1,023 cached positions, context 4,096). ``value`` is decoded tokens per second
@@ -449,6 +450,82 @@ def run_vogilix(args, pk, pk_source):
     return 0
 
 
+def zudepel_config(size: str, layers: int):
+    """Layers of a real model's sizes: lightning and attention layers in turn, every fourth layer reading the keys and values of
+    the attention layer two before it; the first layer dense, the others routed (pass-through choices, groups, a shared expert)."""
+    w, heads, kv_heads, dim, dense, experts, identity, groups, top, ff, shared, vocab = {
+        "mid": (2048, 16, 4, 128, 8192, 32, 4, (4, 2), 4, 1024, 2048, 32768),
+        "wide": (4096, 32, 8, 128, 12288, 64, 8, (8, 4), 6, 1408, 2816, 65536)}[size]
+    import math
+    decay = [math.exp(-2.0 ** (-8.0 * (h + 1) / heads)) for h in range(heads)]
+    moe = {"expert": {"ff": ff}, "kind": "moe", "router": {"experts": experts, "groups": {"count": groups[0], "keep": groups[1]},
+                                                           "identity": identity, "top": top}, "shared": {"ff": shared}}
+    out = []
+    for i in range(layers):
+        mlp = {"ff": dense, "kind": "dense"} if i == 0 else moe
+        if i % 2 == 0:
+            out.append({"mixer": {"decay": decay, "dim": dim, "heads": heads, "vdim": dim}, "mlp": mlp, "type": "lightning"})
+        else:
+            m = {"conv": 4, "dim": dim, "heads": heads, "kv_heads": kv_heads, "rot": {"base": 10000.0, "dims": dim // 2}, "scale": dim ** -0.5,
+                 "vdim": dim}
+            if i % 4 == 3:
+                m["kv_from"] = i - 2
+            out.append({"mixer": m, "mlp": mlp, "type": "attention"})
+    return {"architecture": "Zudepel", "vocab": vocab, "width": w, "norm": {"eps": 1e-6}, "layers": out}
+
+
+def run_zudepel(args, pk, pk_source):
+    """Prefill and decode throughput of the Zudepel design at two sizes, each beside Vogilix layers of the same width, depth,
+    heads, experts and expert sizes (the library's closest model: routed experts on a 32-bit stream); with --timeline also the
+    per-kernel device times of one prompt step and one decode step of the Zudepel model (stderr)."""
+    import torch
+    from tileinfer_b200.config import config_from_dict
+    from tileinfer_b200.engine import Engine
+    layers = args.layers or 8
+    steps, warmup = max(8, min(args.steps, 32)), max(args.warmup, 3)
+    clocks = ClockSampler()
+    clocks.start()
+    out = []
+    for size in ("mid", "wide"):
+        for name, raw in (("zudepel", zudepel_config(size, layers)), ("vogilix", vogilix_config(size, layers))):
+            cfg = config_from_dict(raw)
+            engine = Engine.random(cfg, seed=0, dtype=args.dtype, max_context=4096, max_seqs=64, max_tokens=64 * 1280,
+                                   max_step_tokens=8192)
+            row = {"size": size, "model": name, "layers": layers, "weights_gb": round(engine.weight_bytes() / 1e9, 3),
+                   "cache_bytes_per_position": engine.kv_bytes_per_position()}
+            for tokens in (512, 2048):
+                ms = time_prefill(engine, tokens, cfg.vocab_size, reps=3)
+                row[f"prefill_{tokens}_ms"] = round(ms, 3)
+                row[f"prefill_{tokens}_tok_s"] = round(tokens * 1000.0 / ms, 1)
+            for b in (1, 8, 64):
+                ms, _, launches = time_decode(engine, b, steps, warmup, cfg.vocab_size, count_launches=True)
+                row[f"decode_b{b}_ms"] = round(ms, 4)
+                row[f"decode_b{b}_tok_s"] = round(b * 1000.0 / ms, 1)
+                row[f"decode_b{b}_launches"] = launches
+            engine.check_health()
+            out.append(row)
+            del engine
+            torch.cuda.empty_cache()
+    clock_info = clocks.stop()
+    if args.timeline:
+        from tileinfer_b200.kernels import microbench
+        import contextlib
+        with contextlib.redirect_stdout(sys.stderr):
+            for size in ("mid", "wide"):
+                cfg = config_from_dict(zudepel_config(size, min(layers, 4)))
+                print(f"--- {size}: prompt of 2,048 tokens")
+                microbench.timeline(1, 0, prefill_tokens=2048, config=cfg, first=70)
+                for b in (8, 64):
+                    print(f"--- {size}: decode step of batch {b}")
+                    microbench.timeline(b, 0, config=cfg, first=70 if b == 8 else 1)
+    print(json.dumps({"metric": "prefill and decode of the Zudepel design beside Vogilix layers of equal size", "n_gpus": 1,
+                      "steps": steps, "warmup": warmup, "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
+                      "data": "synthetic: random weights, uniform random token ids",
+                      "config": {"cached_positions": CACHED, "peaks": pk_source, "l2": "every step reads more weights than L2 holds"},
+                      "clocks": clock_info, "rows": out}))
+    return 0
+
+
 def flops_prefill(cfg, n_layers, tokens):
     H, I, D = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
     nq, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
@@ -477,7 +554,7 @@ def main(argv=None) -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (quick checks)")
     ap.add_argument("--timeline", action="store_true", help="--preset vogilix: per-kernel device times of its steps, on stderr")
-    ap.add_argument("--preset", default="8b", choices=["8b", "8b-long", "70b", "sweep", "vogilix"],
+    ap.add_argument("--preset", default="8b", choices=["8b", "8b-long", "70b", "sweep", "vogilix", "zudepel"],
                     help="8b: the headline line (default); 8b-long: 8 unequal sequences of up to 32,768 positions; "
                          "70b: Apertus-70B sizes, 141 GB of weights")
     args = ap.parse_args(argv)
@@ -503,6 +580,8 @@ def main(argv=None) -> int:
         return run_sweep(args, *peaks())
     if args.preset == "vogilix":
         return run_vogilix(args, *peaks())
+    if args.preset == "zudepel":
+        return run_zudepel(args, *peaks())
     cfg_dict = dict(APERTUS_8B)
     full_layers = cfg_dict["num_hidden_layers"]
     if args.layers:

@@ -26,7 +26,7 @@
 
 __device__ __forceinline__ float silu_value(float z) { return z / (1.0f + expf(-z)); }
 
-template <typename T, int DP>
+template <typename T, int DP, bool VECTORS>
 __global__ void __launch_bounds__(LS_COLS* LS_PARTS) lightning_scan_kernel(
     float* __restrict__ o, const T* qkv, long long ld, int q_off, int k_off, int v_off, float* state,
     const float* __restrict__ decay, const int* cu_seqlens, const int* seq_slots, int H, int D, int V, int act) {
@@ -49,9 +49,57 @@ __global__ void __launch_bounds__(LS_COLS* LS_PARTS) lightning_scan_kernel(
         const int d = w + LS_PARTS * i;
         s[i] = (d < D && col < V) ? __ldcg(S + (size_t)d * V + col) : 0.f;
     }
+    // The rows of a round come in 16-byte vectors where the layout allows it, and the next round's are asked for before
+    // this round's arithmetic, so that their way from memory is hidden behind it.
+    constexpr int VEC = 16 / (int)sizeof(T), MAXV = 4;
+    const bool wide = VECTORS && D % VEC == 0 && V % VEC == 0;
+    const int qk_vecs = D / VEC;                        // vectors in a head's row of q (and of k)
+    constexpr int V_VECS = LS_COLS / VEC;               // vectors in the block's 32 columns of v
+    uint4 rq[MAXV], rk[MAXV], rv;
+    auto fetch = [&](int base, int count) {
+#pragma unroll
+        for (int i = 0; i < MAXV; ++i) {
+            const int idx = threadIdx.x + i * (LS_COLS * LS_PARTS);
+            if (idx < count * qk_vecs) {
+                const T* row = qkv + (size_t)(base + idx / qk_vecs) * ld + (size_t)h * D + (idx % qk_vecs) * VEC;
+                rq[i] = __ldcg(reinterpret_cast<const uint4*>(row + q_off));
+                rk[i] = __ldcg(reinterpret_cast<const uint4*>(row + k_off));
+            }
+        }
+        const int idx = threadIdx.x;
+        if (idx < count * V_VECS && col0 + (idx % V_VECS) * VEC < V)
+            rv = __ldcg(reinterpret_cast<const uint4*>(qkv + (size_t)(base + idx / V_VECS) * ld + v_off + (size_t)h * V + col0 + (idx % V_VECS) * VEC));
+    };
+    auto put = [&](float* dst, const uint4& raw) {
+        Vec16<T> v;
+        if constexpr (sizeof(T) == 2) v.unpack(raw);
+        else { v.v[0] = __uint_as_float(raw.x); v.v[1] = __uint_as_float(raw.y); v.v[2] = __uint_as_float(raw.z); v.v[3] = __uint_as_float(raw.w); }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) dst[e] = act ? rnd<T>(silu_value(v.v[e])) : v.v[e];
+    };
+    if (wide && t0 < t1) fetch(t0, min(LS_TOKENS, t1 - t0));
     for (int base = t0; base < t1; base += LS_TOKENS) {
         const int count = min(LS_TOKENS, t1 - base);
         __syncthreads();                                // the last round's readers are done
+        if (wide) {
+#pragma unroll
+            for (int i = 0; i < MAXV; ++i) {
+                const int idx = threadIdx.x + i * (LS_COLS * LS_PARTS);
+                if (idx < count * qk_vecs) {
+                    put(qs + (idx / qk_vecs) * D + (idx % qk_vecs) * VEC, rq[i]);
+                    put(ks + (idx / qk_vecs) * D + (idx % qk_vecs) * VEC, rk[i]);
+                }
+            }
+            const int idx = threadIdx.x;
+            if (idx < count * V_VECS) {
+                float* dst = vs + (idx / V_VECS) * LS_COLS + (idx % V_VECS) * VEC;
+                if (col0 + (idx % V_VECS) * VEC < V) put(dst, rv);
+                else
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) dst[e] = 0.f;
+            }
+            if (base + LS_TOKENS < t1) fetch(base + LS_TOKENS, min(LS_TOKENS, t1 - base - LS_TOKENS));
+        } else {
         for (int e = threadIdx.x; e < count * D; e += blockDim.x) {
             const int t = e / D, d = e % D;
             const T* row = qkv + (size_t)(base + t) * ld + (size_t)h * D + d;
@@ -68,6 +116,7 @@ __global__ void __launch_bounds__(LS_COLS* LS_PARTS) lightning_scan_kernel(
                 if (act) vv = rnd<T>(silu_value(vv));
             }
             vs[t * LS_COLS + c] = vv;
+        }
         }
         __syncthreads();
         for (int t = 0; t < count; ++t) {
@@ -113,11 +162,24 @@ extern "C" int ti_lightning_scan(float* o, const void* qkv, long long ld, int q_
     const dim3 grid((V + LS_COLS - 1) / LS_COLS, H, B);
     const size_t smem = (size_t)(2 * LS_TOKENS * D + LS_TOKENS * LS_COLS + LS_TOKENS * LS_PARTS * LS_COLS) * sizeof(float);
     const int dp = (D + LS_PARTS - 1) / LS_PARTS;
+    // 16-byte loads need every row's pieces on 16-byte borders and at most four vectors of q per thread and round.
 #define LS_LAUNCH(DP)                                                                                                                \
-    ti_launch(lightning_scan_kernel<T, DP>, grid, dim3(LS_COLS* LS_PARTS), smem, stream, o, (const T*)qkv, ld, q_off, k_off, v_off, state, \
-              decay, cu_seqlens, seq_slots, H, D, V, act)
+    do {                                                                                                                             \
+        constexpr int VEC = 16 / (int)sizeof(T);                                                                                     \
+        const bool vectors = aligned16(qkv) && ld % VEC == 0 && q_off % VEC == 0 && k_off % VEC == 0 && v_off % VEC == 0 &&          \
+                             LS_TOKENS * (D / VEC) <= 4 * LS_COLS * LS_PARTS;                                                        \
+        if (vectors)                                                                                                                 \
+            ti_launch(lightning_scan_kernel<T, DP, true>, grid, dim3(LS_COLS* LS_PARTS), smem, stream, o, (const T*)qkv, ld, q_off, k_off, v_off,   \
+                      state, decay, cu_seqlens, seq_slots, H, D, V, act);                                                            \
+        else                                                                                                                         \
+            ti_launch(lightning_scan_kernel<T, DP, false>, grid, dim3(LS_COLS* LS_PARTS), smem, stream, o, (const T*)qkv, ld, q_off, k_off, v_off,  \
+                      state, decay, cu_seqlens, seq_slots, H, D, V, act);                                                            \
+    } while (0)
     TI_DISPATCH_DTYPE(dtype, {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(lightning_scan_kernel<T, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (smem > 48 * 1024) {
+            cudaFuncSetAttribute(lightning_scan_kernel<T, 32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaFuncSetAttribute(lightning_scan_kernel<T, 32, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        }
         if (dp <= 4) LS_LAUNCH(4);
         else if (dp <= 8) LS_LAUNCH(8);
         else if (dp <= 16) LS_LAUNCH(16);

@@ -365,13 +365,59 @@ __global__ void expert_combine_kernel(T* __restrict__ out, const T* y, const int
     }
 }
 
+// The same with 16 bytes of outputs per thread (the sums in the same order).
+template <typename T>
+__global__ void expert_combine_vec_kernel(T* __restrict__ out, const T* y, const int* pair_row, const float* scores, const T* shared,
+                                          const T* h, const float* pass_weight, int top, int width, int scale_output) {
+    constexpr int N = Vec16<T>::N;
+    const int t = blockIdx.x;
+    pdl_enter();
+    for (int i = threadIdx.x * N; i < width; i += blockDim.x * N) {
+        float a[N];
+#pragma unroll
+        for (int e = 0; e < N; ++e) a[e] = 0.f;
+        for (int j = 0; j < top; ++j) {
+            const int p = t * top + j;
+            const int row = __ldcg(pair_row + p);
+            if (row < 0) continue;
+            const float w = scale_output ? __ldcg(scores + p) : 1.0f;
+            Vec16<T> v;
+            v.load_cg(y + (size_t)row * width + i);
+#pragma unroll
+            for (int e = 0; e < N; ++e) a[e] += scale_output ? w * v.v[e] : v.v[e];
+        }
+        Vec16<T> v;
+        if (shared != nullptr) {
+            v.load_cg(shared + (size_t)t * width + i);
+#pragma unroll
+            for (int e = 0; e < N; ++e) a[e] += v.v[e];
+        }
+        if (pass_weight != nullptr) {
+            const float w = __ldcg(pass_weight + t);
+            v.load_cg(h + (size_t)t * width + i);
+#pragma unroll
+            for (int e = 0; e < N; ++e) a[e] = fmaf(w, v.v[e], a[e]);
+        }
+#pragma unroll
+        for (int e = 0; e < N; ++e) v.v[e] = a[e];
+        v.store(out + (size_t)t * width + i);
+    }
+}
+
 // `pass_weight` [n] with `h` [n, width] (both or neither): pass_weight[t] * h[t] is added, the share of choices that hand their
 // input through unchanged.
 extern "C" int ti_expert_combine(void* out, const void* y, const int* pair_row, const float* scores, const void* shared, const void* h,
                                  const float* pass_weight, int n, int top, int width, int scale_output, int dtype, cudaStream_t stream) {
     if (n == 0) return 0;
     TI_REQUIRE((h != nullptr) == (pass_weight != nullptr), "expert_combine: the passed-through share needs both its weights and the input");
-    TI_DISPATCH_DTYPE(dtype, (ti_launch(expert_combine_kernel<T>, dim3(n), dim3(width >= 1024 ? 256 : 128), 0, stream, (T*)out, (const T*)y,
-                                        pair_row, scores, (const T*)shared, (const T*)h, pass_weight, top, width, scale_output)));
+    TI_DISPATCH_DTYPE(dtype, {
+        constexpr int N = Vec16<T>::N;
+        if (width % N == 0 && aligned16(out) && aligned16(y) && aligned16(shared) && aligned16(h))
+            ti_launch(expert_combine_vec_kernel<T>, dim3(n), dim3(width >= 2048 ? 256 : 128), 0, stream, (T*)out, (const T*)y, pair_row, scores,
+                      (const T*)shared, (const T*)h, pass_weight, top, width, scale_output);
+        else
+            ti_launch(expert_combine_kernel<T>, dim3(n), dim3(width >= 1024 ? 256 : 128), 0, stream, (T*)out, (const T*)y, pair_row, scores,
+                      (const T*)shared, (const T*)h, pass_weight, top, width, scale_output);
+    });
     return ti_check_launch("expert_combine");
 }

@@ -302,6 +302,56 @@ __global__ void sum_add_norm32_kernel(float* x, const T* d1, const float* p1, in
     }
 }
 
+// The same for bfloat16 rows with four elements per thread and step (16-byte accesses of the stream and of partial sums, 8-byte
+// accesses of the rows); the sums in the same order.
+__device__ __forceinline__ void branch_value4(const bf16* d, const float* partials, int n_partials, size_t stride, size_t at, float (&v)[4]) {
+    if (partials != nullptr) {
+        float4 t = __ldcg(reinterpret_cast<const float4*>(partials + at));
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+        for (int s = 1; s < n_partials; ++s) {
+            t = __ldcg(reinterpret_cast<const float4*>(partials + (size_t)s * stride + at));
+            v[0] += t.x; v[1] += t.y; v[2] += t.z; v[3] += t.w;
+        }
+    } else if (d != nullptr) {
+        load4(d + at, v);
+    } else {
+        v[0] = v[1] = v[2] = v[3] = 0.f;
+    }
+}
+
+__global__ void sum_add_norm32_vec_kernel(float* x, const bf16* d1, const float* p1, int n1, size_t s1, const bf16* d2, const float* p2, int n2,
+                                          size_t s2, bf16* __restrict__ h, const bf16* __restrict__ w_out, int offset_out, float eps_out, int size) {
+    extern __shared__ float row_d[];
+    __shared__ float scratch[33];
+    float* row = x + (size_t)blockIdx.x * size;
+    float ss = 0.f;
+    pdl_enter();
+    for (int i = threadIdx.x * 4; i < size; i += blockDim.x * 4) {
+        const size_t at = (size_t)blockIdx.x * size + i;
+        float a[4], b[4];
+        branch_value4(d1, p1, n1, s1, at, a);
+        branch_value4(d2, p2, n2, s2, at, b);
+        const float4 xv = __ldcg(reinterpret_cast<const float4*>(row + i));
+        const float v[4] = {xv.x + (a[0] + b[0]), xv.y + (a[1] + b[1]), xv.z + (a[2] + b[2]), xv.w + (a[3] + b[3])};
+        *reinterpret_cast<float4*>(row + i) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(row_d + i) = make_float4(v[0], v[1], v[2], v[3]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ss = fmaf(v[e], v[e], ss);
+    }
+    if (h == nullptr) return;
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)size + eps_out);
+    bf16* dst = h + (size_t)blockIdx.x * size;
+    for (int i = threadIdx.x * 4; i < size; i += blockDim.x * 4) {
+        const float4 t = *reinterpret_cast<const float4*>(row_d + i);
+        float g[4], v[4] = {t.x, t.y, t.z, t.w};
+        load4w(w_out + i, g);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] = v[e] * inv * (offset_out ? 1.0f + g[e] : g[e]);
+        store4(dst + i, v);
+    }
+}
+
 extern "C" int ti_sum_add_norm32(float* x, const void* d1, const float* p1, int n1, long long s1, const void* d2, const float* p2, int n2, long long s2,
                                  void* h, const void* w_out, int offset_out, float eps_out, int n_rows, int size, int dtype, cudaStream_t stream) {
     if (n_rows == 0) return 0;
@@ -311,6 +361,13 @@ extern "C" int ti_sum_add_norm32(float* x, const void* d1, const float* p1, int 
     const size_t smem = (size_t)size * sizeof(float);
     TI_DISPATCH_DTYPE(dtype, {
         if (smem > 48 * 1024) cudaFuncSetAttribute(sum_add_norm32_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        const bool vec = sizeof(T) == 2 && size % 4 == 0 && smem <= 48 * 1024 && aligned16(x) && (p1 == nullptr || (aligned16(p1) && s1 % 4 == 0)) &&
+                         (p2 == nullptr || (aligned16(p2) && s2 % 4 == 0)) &&
+                         (((uintptr_t)d1 | (uintptr_t)d2 | (uintptr_t)h | (uintptr_t)w_out) & 7) == 0;
+        if (vec)
+            ti_launch(sum_add_norm32_vec_kernel, dim3(n_rows), dim3(size >= 2048 ? 256 : 128), smem, stream, x, (const bf16*)d1, p1, n1, (size_t)s1,
+                      (const bf16*)d2, p2, n2, (size_t)s2, (bf16*)h, (const bf16*)w_out, offset_out, eps_out, size);
+        else
         ti_launch(sum_add_norm32_kernel<T>, dim3(n_rows), dim3(row_threads(size)), smem, stream, x, (const T*)d1, p1, n1, (size_t)s1, (const T*)d2, p2, n2,
                   (size_t)s2, (T*)h, (const T*)w_out, offset_out, eps_out, size);
     });

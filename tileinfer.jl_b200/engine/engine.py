@@ -240,8 +240,17 @@ class Engine:
                 from ..kernels import library
                 before = library.launch_count
                 graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph):
-                    self.model.forward(ctx, self.cache, logits)
+                # No garbage collection while the stream is capturing: an object freed then (another engine's pinned
+                # buffers, say) would make a CUDA call that invalidates the capture.
+                import gc
+                collecting = gc.isenabled()
+                gc.disable()
+                try:
+                    with torch.cuda.graph(graph):
+                        self.model.forward(ctx, self.cache, logits)
+                finally:
+                    if collecting:
+                        gc.enable()
                 self._graphs[B] = (graph, self.rt.generation)
                 self._graph_launches[B] = library.launch_count - before
             else:
