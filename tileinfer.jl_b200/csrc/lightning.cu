@@ -12,10 +12,12 @@
 //                    the output gate; the input of the output projection.
 //
 // The scan: the columns of S are independent (column j of S sees v_t[j] only), so a block owns 32 columns of one
-// (sequence, head) and walks the sequence's tokens in order; its 8 warps split the rows of S (warp w owns rows w, w + 8,
-// ...), a lane owns one column, the state lives in registers. Tokens are staged 16 at a time in shared memory; the
-// warps' partial sums of o meet there once per 16 tokens. Every sum's order depends on the sizes alone, and a token's
-// result on the sequence's earlier tokens alone, so how a prompt is cut into steps or batched changes no bit.
+// (sequence, head) and walks the sequence's tokens in order; its 8 warps split the rows of S (warp w owns DP rows in a
+// row, read from shared memory four at a time), a lane owns one column, the state lives in registers. Tokens are staged 16 at a time in shared memory; the
+// warps' partial sums of o meet there once per 16 tokens. A launch of few blocks (one prompt, few heads) shares the rows of S
+// out between two blocks per column block, whose two shares of o are added in global memory. A token's result depends on
+// the sequence's earlier tokens alone; the order of its sums depends on the sizes and on whether the launch was shared
+// out, so results agree to rounding, not bit for bit, between a prompt alone and the same prompt in a large batch.
 // Everything is 32-bit arithmetic; nothing of the state, the decay or o is rounded.
 #include "common.cuh"
 
@@ -29,14 +31,16 @@ __device__ __forceinline__ float silu_value(float z) { return z / (1.0f + expf(-
 template <typename T, int DP, bool VECTORS>
 __global__ void __launch_bounds__(LS_COLS* LS_PARTS) lightning_scan_kernel(
     float* __restrict__ o, const T* qkv, long long ld, int q_off, int k_off, int v_off, float* state,
-    const float* __restrict__ decay, const int* cu_seqlens, const int* seq_slots, int H, int D, int V, int act) {
+    const float* __restrict__ decay, const int* cu_seqlens, const int* seq_slots, int H, int D, int V, int act, int split) {
     extern __shared__ float smem[];
     float* qs = smem;                                   // [LS_TOKENS][D]
     float* ks = qs + LS_TOKENS * D;                     // [LS_TOKENS][D]
     float* vs = ks + LS_TOKENS * D;                     // [LS_TOKENS][LS_COLS]
     float* part = vs + LS_TOKENS * LS_COLS;             // [LS_TOKENS][LS_PARTS][LS_COLS]
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    const int col0 = blockIdx.x * LS_COLS, h = blockIdx.y, b = blockIdx.z;
+    // With `split` > 1 the rows of S are shared out among that many blocks, whose shares of o are added up in global memory.
+    const int col0 = (blockIdx.x / split) * LS_COLS, h = blockIdx.y, b = blockIdx.z;
+    const int rows_per = (D + split - 1) / split, row0 = (blockIdx.x % split) * rows_per, row1 = min(D, row0 + rows_per);
     const int col = col0 + lane;
     const float a = decay[h];
     pdl_enter();
@@ -46,8 +50,8 @@ __global__ void __launch_bounds__(LS_COLS* LS_PARTS) lightning_scan_kernel(
     float s[DP];
 #pragma unroll
     for (int i = 0; i < DP; ++i) {
-        const int d = w + LS_PARTS * i;
-        s[i] = (d < D && col < V) ? __ldcg(S + (size_t)d * V + col) : 0.f;
+        const int d = row0 + w * DP + i;
+        s[i] = (d < row1 && col < V) ? __ldcg(S + (size_t)d * V + col) : 0.f;
     }
     // The rows of a round come in 16-byte vectors where the layout allows it, and the next round's are asked for before
     // this round's arithmetic, so that their way from memory is hidden behind it.
@@ -75,7 +79,8 @@ __global__ void __launch_bounds__(LS_COLS* LS_PARTS) lightning_scan_kernel(
         if constexpr (sizeof(T) == 2) v.unpack(raw);
         else { v.v[0] = __uint_as_float(raw.x); v.v[1] = __uint_as_float(raw.y); v.v[2] = __uint_as_float(raw.z); v.v[3] = __uint_as_float(raw.w); }
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) dst[e] = act ? rnd<T>(silu_value(v.v[e])) : v.v[e];
+        for (int e = 0; e < VEC; ++e)           // (16-bit rows: the fast exponential and division are far below their rounding)
+            dst[e] = !act ? v.v[e] : sizeof(T) == 2 ? rnd<T>(__fdividef(v.v[e], 1.0f + __expf(-v.v[e]))) : silu_value(v.v[e]);
     };
     if (wide && t0 < t1) fetch(t0, min(LS_TOKENS, t1 - t0));
     for (int base = t0; base < t1; base += LS_TOKENS) {
@@ -119,20 +124,42 @@ __global__ void __launch_bounds__(LS_COLS* LS_PARTS) lightning_scan_kernel(
         }
         }
         __syncthreads();
-        for (int t = 0; t < count; ++t) {
+        // One token: the state's rows of this warp move on and give their share of o. Four partial sums keep the chain of
+        // dependent additions short; the order of a token's sum still depends on the sizes alone.
+        auto token = [&](int t) {
             const float vt = vs[t * LS_COLS + lane];
             const float* qt = qs + t * D;
             const float* kt = ks + t * D;
-            float acc = 0.f;
+            float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+            if (D % 4 == 0 && rows_per % 4 == 0) {       // (DP is a multiple of 4: four rows' k and q per shared-memory read)
 #pragma unroll
-            for (int i = 0; i < DP; ++i) {
-                const int d = w + LS_PARTS * i;
-                if (d < D) {
-                    s[i] = fmaf(a, s[i], kt[d] * vt);
-                    acc = fmaf(s[i], qt[d], acc);
+                for (int i = 0; i < DP; i += 4) {
+                    const int d = row0 + w * DP + i;
+                    if (d < row1) {
+                        const float4 k4 = *reinterpret_cast<const float4*>(kt + d), q4 = *reinterpret_cast<const float4*>(qt + d);
+                        s[i] = fmaf(a, s[i], k4.x * vt); acc0 = fmaf(s[i], q4.x, acc0);
+                        s[i + 1] = fmaf(a, s[i + 1], k4.y * vt); acc1 = fmaf(s[i + 1], q4.y, acc1);
+                        s[i + 2] = fmaf(a, s[i + 2], k4.z * vt); acc2 = fmaf(s[i + 2], q4.z, acc2);
+                        s[i + 3] = fmaf(a, s[i + 3], k4.w * vt); acc3 = fmaf(s[i + 3], q4.w, acc3);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < DP; ++i) {
+                    const int d = row0 + w * DP + i;
+                    if (d < row1) {
+                        s[i] = fmaf(a, s[i], kt[d] * vt);
+                        acc0 = fmaf(s[i], qt[d], acc0);
+                    }
                 }
             }
-            part[(t * LS_PARTS + w) * LS_COLS + lane] = acc;
+            part[(t * LS_PARTS + w) * LS_COLS + lane] = (acc0 + acc1) + (acc2 + acc3);
+        };
+        if (count == LS_TOKENS) {
+#pragma unroll 4
+            for (int t = 0; t < LS_TOKENS; ++t) token(t);
+        } else {
+            for (int t = 0; t < count; ++t) token(t);
         }
         __syncthreads();
         for (int e = threadIdx.x; e < count * LS_COLS; e += blockDim.x) {
@@ -141,45 +168,51 @@ __global__ void __launch_bounds__(LS_COLS* LS_PARTS) lightning_scan_kernel(
             float sum = 0.f;
 #pragma unroll
             for (int p = 0; p < LS_PARTS; ++p) sum += part[(t * LS_PARTS + p) * LS_COLS + c];
-            o[(size_t)(base + t) * H * V + (size_t)h * V + col0 + c] = sum;
+            float* dst = o + (size_t)(base + t) * H * V + (size_t)h * V + col0 + c;
+            if (split > 1) atomicAdd(dst, sum);         // o was zeroed; with two addends the sum does not depend on their order
+            else *dst = sum;
         }
     }
 #pragma unroll
     for (int i = 0; i < DP; ++i) {
-        const int d = w + LS_PARTS * i;
-        if (d < D && col < V) S[(size_t)d * V + col] = s[i];
+        const int d = row0 + w * DP + i;
+        if (d < row1 && col < V) S[(size_t)d * V + col] = s[i];
     }
 }
 
 // o [n, H * V] float; qkv [n, ld] of T with the heads' queries from column q_off on (H * D of them), keys from k_off, values
-// from v_off (H * V); state [slots, H, D, V] float; decay [H] float; cu_seqlens [B + 1], seq_slots [B]. act: 1 = SiLU.
+// from v_off (H * V); state [slots, H, D, V] float; decay [H] float; cu_seqlens [B + 1], seq_slots [B] (n_tokens in all). act: 1 = SiLU.
 extern "C" int ti_lightning_scan(float* o, const void* qkv, long long ld, int q_off, int k_off, int v_off, float* state, const float* decay,
-                                 const int* cu_seqlens, const int* seq_slots, int B, int H, int D, int V, int act, int dtype,
+                                 const int* cu_seqlens, const int* seq_slots, int n_tokens, int B, int H, int D, int V, int act, int dtype,
                                  cudaStream_t stream) {
     if (B == 0) return 0;
     TI_REQUIRE(H > 0 && D > 0 && V > 0 && D <= LS_MAX_DIM, "lightning_scan: %d heads of %d x %d (the key size is at most %d)", H, D, V, LS_MAX_DIM);
     TI_REQUIRE(H <= 65535 && B <= 65535, "lightning_scan: %d heads, %d sequences", H, B);
-    const dim3 grid((V + LS_COLS - 1) / LS_COLS, H, B);
+    // A launch with few blocks (one prompt of a model with few heads) shares the rows of S out between two blocks each.
+    const int col_blocks = (V + LS_COLS - 1) / LS_COLS;
+    const int split = ((long long)col_blocks * H * B < 100 && D >= 16) ? 2 : 1;
+    if (split > 1 && cudaMemsetAsync(o, 0, (size_t)n_tokens * H * V * sizeof(float), stream) != cudaSuccess) return ti_fail("lightning_scan: memset failed");
+    const dim3 grid(col_blocks * split, H, B);
     const size_t smem = (size_t)(2 * LS_TOKENS * D + LS_TOKENS * LS_COLS + LS_TOKENS * LS_PARTS * LS_COLS) * sizeof(float);
-    const int dp = (D + LS_PARTS - 1) / LS_PARTS;
+    const int dp = ((D + split - 1) / split + LS_PARTS - 1) / LS_PARTS;
     // 16-byte loads need every row's pieces on 16-byte borders and at most four vectors of q per thread and round.
 #define LS_LAUNCH(DP)                                                                                                                \
     do {                                                                                                                             \
         constexpr int VEC = 16 / (int)sizeof(T);                                                                                     \
         const bool vectors = aligned16(qkv) && ld % VEC == 0 && q_off % VEC == 0 && k_off % VEC == 0 && v_off % VEC == 0 &&          \
                              LS_TOKENS * (D / VEC) <= 4 * LS_COLS * LS_PARTS;                                                        \
+        if (smem > 48 * 1024) {                                                                                                      \
+            cudaFuncSetAttribute(lightning_scan_kernel<T, DP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
+            cudaFuncSetAttribute(lightning_scan_kernel<T, DP, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+        }                                                                                                                            \
         if (vectors)                                                                                                                 \
             ti_launch(lightning_scan_kernel<T, DP, true>, grid, dim3(LS_COLS* LS_PARTS), smem, stream, o, (const T*)qkv, ld, q_off, k_off, v_off,   \
-                      state, decay, cu_seqlens, seq_slots, H, D, V, act);                                                            \
+                      state, decay, cu_seqlens, seq_slots, H, D, V, act, split);                                                     \
         else                                                                                                                         \
             ti_launch(lightning_scan_kernel<T, DP, false>, grid, dim3(LS_COLS* LS_PARTS), smem, stream, o, (const T*)qkv, ld, q_off, k_off, v_off,  \
-                      state, decay, cu_seqlens, seq_slots, H, D, V, act);                                                            \
+                      state, decay, cu_seqlens, seq_slots, H, D, V, act, split);                                                     \
     } while (0)
     TI_DISPATCH_DTYPE(dtype, {
-        if (smem > 48 * 1024) {
-            cudaFuncSetAttribute(lightning_scan_kernel<T, 32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            cudaFuncSetAttribute(lightning_scan_kernel<T, 32, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        }
         if (dp <= 4) LS_LAUNCH(4);
         else if (dp <= 8) LS_LAUNCH(8);
         else if (dp <= 16) LS_LAUNCH(16);

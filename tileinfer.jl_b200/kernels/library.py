@@ -184,7 +184,7 @@ _SIGNATURES.update({
 # A state carried from token to token (linear attention with decay), projections through a short convolution, two sublayers
 # added at once, routers with more rules, unclamped gated units.
 _SIGNATURES.update({
-    "ti_lightning_scan": [_P, _P, _L, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "ti_lightning_scan": [_P, _P, _L, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "ti_lightning_out": [_P, _P, _P, _L, _P, _F, _I, _I, _I, _P],
     "ti_conv_attention_inputs": [_P, _L, _P, _P, _I, _P, _P, _P, _F, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I,
                                  _I, _P],

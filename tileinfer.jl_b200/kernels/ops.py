@@ -416,7 +416,7 @@ def lightning_scan(o, rows, q_off, k_off, v_off, state, decay, cu_seqlens, seq_s
     if rows.stride(1) != 1 or tuple(state.shape[1:]) != (heads, dim, vdim) or decay.numel() != heads:
         raise KernelError(f"lightning_scan: rows {tuple(rows.shape)}, state {tuple(state.shape)} for {heads} heads of {dim} x {vdim}")
     check(lib().ti_lightning_scan(o.data_ptr(), rows.data_ptr(), rows.stride(0), q_off, k_off, v_off, state.data_ptr(), decay.data_ptr(),
-                                  cu_seqlens.data_ptr(), seq_slots.data_ptr(), batch, heads, dim, vdim, int(bool(act)), dtype_code(rows.dtype),
+                                  cu_seqlens.data_ptr(), seq_slots.data_ptr(), rows.shape[0], batch, heads, dim, vdim, int(bool(act)), dtype_code(rows.dtype),
                                   _stream()), "lightning_scan")
 
 
