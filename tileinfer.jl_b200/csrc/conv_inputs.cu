@@ -26,7 +26,7 @@ __device__ __forceinline__ int sequence_of(const int* cu, int B, int t) {
     return lo;
 }
 
-template <typename T>
+template <typename T, int TAPS>
 __global__ void __launch_bounds__(CI_THREADS) conv_attention_inputs_kernel(
     const T* proj, long long ld, const T* __restrict__ bias, const T* __restrict__ conv, int taps, const float* state,
     const T* __restrict__ q_norm_w, const T* __restrict__ k_norm_w, float eps, const float* __restrict__ cos_sin, int rotary,
@@ -44,21 +44,37 @@ __global__ void __launch_bounds__(CI_THREADS) conv_attention_inputs_kernel(
     const int slot = __ldcg(seq_slots + b);
     const float* hist = state + (size_t)slot * (taps > 1 ? taps - 1 : 0) * C;
     pdl_enter();
+    // A channel's taps: all their loads (the rows they read, from the step's own projection or from the state, and their
+    // weights) are issued before the first is used. With the number of taps known at compile time (TAPS >= 0) the loop
+    // is unrolled and two channels are in flight per thread: a step of few tokens has nothing else to hide latency behind.
     float ssq = 0.f, ssk = 0.f;
+    const int ntaps = TAPS >= 0 ? TAPS : taps;
+    auto tap_input = [&](int c, int j, float bc) -> float {
+        const int back = ntaps - 1 - j, pj = p - back;
+        if (pj >= p0) return rnd<T>(to_f32(__ldcg(proj + (size_t)(t - back) * ld + c)) + bc);
+        if (pj >= 0) return __ldcg(hist + (size_t)(ntaps - 1 - (p0 - pj)) * C + c);
+        return 0.f;
+    };
+#pragma unroll 2
     for (int c = threadIdx.x; c < C; c += CI_THREADS) {
         const float bc = bias != nullptr ? to_f32(bias[c]) : 0.f;
         float acc;
-        if (taps <= 0) {
+        if (ntaps <= 0) {
             acc = rnd<T>(to_f32(__ldcg(proj + (size_t)t * ld + c)) + bc);
+        } else if (TAPS > 0) {
+            float u[TAPS > 0 ? TAPS : 1], w[TAPS > 0 ? TAPS : 1];
+#pragma unroll
+            for (int j = 0; j < TAPS; ++j) {
+                u[j] = tap_input(c, j, bc);
+                w[j] = to_f32(conv[(size_t)c * TAPS + j]);
+            }
+            acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < TAPS; ++j) acc = fmaf(w[j], u[j], acc);
+            acc = rnd<T>(acc);
         } else {
             acc = 0.f;
-            for (int j = 0; j < taps; ++j) {
-                const int back = taps - 1 - j, pj = p - back;
-                float u = 0.f;
-                if (pj >= p0) u = rnd<T>(to_f32(__ldcg(proj + (size_t)(t - back) * ld + c)) + bc);
-                else if (pj >= 0) u = __ldcg(hist + (size_t)(taps - 1 - (p0 - pj)) * C + c);
-                acc = fmaf(to_f32(conv[(size_t)c * taps + j]), u, acc);
-            }
+            for (int j = 0; j < ntaps; ++j) acc = fmaf(to_f32(conv[(size_t)c * ntaps + j]), tap_input(c, j, bc), acc);
             acc = rnd<T>(acc);
         }
         y[c] = acc;
@@ -117,12 +133,24 @@ extern "C" int ti_conv_attention_inputs(const void* proj, long long ld, const vo
     const int C = nq * D + (write_kv ? nkv * (D + V) : 0);
     const size_t smem = (size_t)C * sizeof(float);
     TI_REQUIRE(smem <= 160 * 1024, "conv_attention_inputs: %d channels", C);
+#define CI_LAUNCH(TAPS)                                                                                                                       \
+    do {                                                                                                                                      \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(conv_attention_inputs_kernel<T, TAPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        ti_launch(conv_attention_inputs_kernel<T, TAPS>, dim3(n), dim3(CI_THREADS), smem, stream, (const T*)proj, ld, (const T*)bias, (const T*)conv,  \
+                  taps, state, (const T*)q_norm_w, (const T*)k_norm_w, eps, cos_sin, rotary, (T*)q_out, (T*)k_cache, (T*)v_cache, positions,       \
+                  slot_map, cu_seqlens, seq_slots, kv_lens, B, nq, nkv, D, V, Dp, page_size, write_kv);                                          \
+    } while (0)
     TI_DISPATCH_DTYPE(dtype, {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(conv_attention_inputs_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        ti_launch(conv_attention_inputs_kernel<T>, dim3(n), dim3(CI_THREADS), smem, stream, (const T*)proj, ld, (const T*)bias, (const T*)conv, taps,
-                  state, (const T*)q_norm_w, (const T*)k_norm_w, eps, cos_sin, rotary, (T*)q_out, (T*)k_cache, (T*)v_cache, positions, slot_map,
-                  cu_seqlens, seq_slots, kv_lens, B, nq, nkv, D, V, Dp, page_size, write_kv);
+        switch (taps) {
+            case 0: CI_LAUNCH(0); break;
+            case 1: CI_LAUNCH(1); break;
+            case 2: CI_LAUNCH(2); break;
+            case 3: CI_LAUNCH(3); break;
+            case 4: CI_LAUNCH(4); break;
+            default: CI_LAUNCH(-1); break;
+        }
     });
+#undef CI_LAUNCH
     return ti_check_launch("conv_attention_inputs");
 }
 
