@@ -12,7 +12,7 @@
 //                    the output gate; the input of the output projection.
 //
 // The scan: the columns of S are independent (column j of S sees v_t[j] only), so a block owns 32 columns of one
-// (sequence, head) and walks the sequence's tokens in order; its 8 warps split the rows of S (warp w owns DP rows in a
+// (sequence, head) and walks the sequence's tokens in order; its 8 or 16 warps split the rows of S (warp w owns DP rows in a
 // row, read from shared memory four at a time), a lane owns one column, the state lives in registers. Tokens are staged 16 at a time in shared memory; the
 // warps' partial sums of o meet there once per 16 tokens. A launch of few blocks (one prompt, few heads) shares the rows of S
 // out between two blocks per column block, whose two shares of o are added in global memory. A token's result depends on
@@ -22,13 +22,12 @@
 #include "common.cuh"
 
 #define LS_COLS 32
-#define LS_PARTS 8
 #define LS_TOKENS 16
 #define LS_MAX_DIM 256
 
 __device__ __forceinline__ float silu_value(float z) { return z / (1.0f + expf(-z)); }
 
-template <typename T, int DP, bool VECTORS>
+template <typename T, int DP, bool VECTORS, int LS_PARTS>
 __global__ void __launch_bounds__(LS_COLS* LS_PARTS) lightning_scan_kernel(
     float* __restrict__ o, const T* qkv, long long ld, int q_off, int k_off, int v_off, float* state,
     const float* __restrict__ decay, const int* cu_seqlens, const int* seq_slots, int H, int D, int V, int act, int split) {
@@ -193,24 +192,32 @@ extern "C" int ti_lightning_scan(float* o, const void* qkv, long long ld, int q_
     const int split = ((long long)col_blocks * H * B < 100 && D >= 16) ? 2 : 1;
     if (split > 1 && cudaMemsetAsync(o, 0, (size_t)n_tokens * H * V * sizeof(float), stream) != cudaSuccess) return ti_fail("lightning_scan: memset failed");
     const dim3 grid(col_blocks * split, H, B);
-    const size_t smem = (size_t)(2 * LS_TOKENS * D + LS_TOKENS * LS_COLS + LS_TOKENS * LS_PARTS * LS_COLS) * sizeof(float);
-    const int dp = ((D + split - 1) / split + LS_PARTS - 1) / LS_PARTS;
+    // Few blocks walking long sequences are bound by latency: 16 warps a block then (each with half the rows); many blocks, or
+    // one-token steps, which are bound by reading and writing the state, run better with 8.
+    const int parts = ((long long)col_blocks * split * H * B <= 160 && n_tokens >= 64 * B) ? 16 : 8;
+    const size_t smem = (size_t)(2 * LS_TOKENS * D + LS_TOKENS * LS_COLS + LS_TOKENS * parts * LS_COLS) * sizeof(float);
+    const int dp = ((D + split - 1) / split + parts - 1) / parts;
     // 16-byte loads need every row's pieces on 16-byte borders and at most four vectors of q per thread and round.
-#define LS_LAUNCH(DP)                                                                                                                \
+#define LS_LAUNCH2(DP, PARTS)                                                                                                        \
     do {                                                                                                                             \
         constexpr int VEC = 16 / (int)sizeof(T);                                                                                     \
         const bool vectors = aligned16(qkv) && ld % VEC == 0 && q_off % VEC == 0 && k_off % VEC == 0 && v_off % VEC == 0 &&          \
-                             LS_TOKENS * (D / VEC) <= 4 * LS_COLS * LS_PARTS;                                                        \
+                             LS_TOKENS * (D / VEC) <= 4 * LS_COLS * PARTS;                                                           \
         if (smem > 48 * 1024) {                                                                                                      \
-            cudaFuncSetAttribute(lightning_scan_kernel<T, DP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
-            cudaFuncSetAttribute(lightning_scan_kernel<T, DP, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+            cudaFuncSetAttribute(lightning_scan_kernel<T, DP, true, PARTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            cudaFuncSetAttribute(lightning_scan_kernel<T, DP, false, PARTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         }                                                                                                                            \
         if (vectors)                                                                                                                 \
-            ti_launch(lightning_scan_kernel<T, DP, true>, grid, dim3(LS_COLS* LS_PARTS), smem, stream, o, (const T*)qkv, ld, q_off, k_off, v_off,   \
-                      state, decay, cu_seqlens, seq_slots, H, D, V, act, split);                                                     \
+            ti_launch(lightning_scan_kernel<T, DP, true, PARTS>, grid, dim3(LS_COLS* PARTS), smem, stream, o, (const T*)qkv, ld, q_off, k_off,    \
+                      v_off, state, decay, cu_seqlens, seq_slots, H, D, V, act, split);                                              \
         else                                                                                                                         \
-            ti_launch(lightning_scan_kernel<T, DP, false>, grid, dim3(LS_COLS* LS_PARTS), smem, stream, o, (const T*)qkv, ld, q_off, k_off, v_off,  \
-                      state, decay, cu_seqlens, seq_slots, H, D, V, act, split);                                                     \
+            ti_launch(lightning_scan_kernel<T, DP, false, PARTS>, grid, dim3(LS_COLS* PARTS), smem, stream, o, (const T*)qkv, ld, q_off, k_off,   \
+                      v_off, state, decay, cu_seqlens, seq_slots, H, D, V, act, split);                                              \
+    } while (0)
+#define LS_LAUNCH(DP)                        \
+    do {                                     \
+        if (parts == 16) LS_LAUNCH2(DP, 16); \
+        else LS_LAUNCH2(DP, 8);              \
     } while (0)
     TI_DISPATCH_DTYPE(dtype, {
         if (dp <= 4) LS_LAUNCH(4);
@@ -218,6 +225,7 @@ extern "C" int ti_lightning_scan(float* o, const void* qkv, long long ld, int q_
         else if (dp <= 16) LS_LAUNCH(16);
         else LS_LAUNCH(32);
     });
+#undef LS_LAUNCH2
 #undef LS_LAUNCH
     return ti_check_launch("lightning_scan");
 }
