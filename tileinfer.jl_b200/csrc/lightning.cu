@@ -179,6 +179,63 @@ __global__ void __launch_bounds__(LS_COLS* LS_PARTS) lightning_scan_kernel(
     }
 }
 
+// One token per sequence: the step reads and writes every state once and is bound by that traffic. A block owns 128 columns
+// of one (sequence, head): a lane owns four of them (16 bytes of a row), the warps take the rows in turn with several rows'
+// loads in flight, and their shares of o meet in shared memory. The arithmetic per element is the scan's.
+#define LT_WARPS 8
+template <typename T>
+__global__ void __launch_bounds__(LT_WARPS * 32) lightning_token_kernel(float* __restrict__ o, const T* qkv, long long ld, int q_off, int k_off,
+                                                                        int v_off, float* state, const float* __restrict__ decay,
+                                                                        const int* seq_slots, int H, int D, int V, int act) {
+    extern __shared__ float smem[];
+    float* qs = smem;                                   // [D]
+    float* ks = qs + D;                                 // [D]
+    float* part = ks + D;                               // [LT_WARPS][128]
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int col = blockIdx.x * 128 + lane * 4, h = blockIdx.y, b = blockIdx.z;
+    const float a = decay[h];
+    pdl_enter();
+    const T* row = qkv + (size_t)b * ld;
+    for (int d = threadIdx.x; d < D; d += LT_WARPS * 32) {
+        float qv = to_f32(__ldcg(row + q_off + (size_t)h * D + d)), kv = to_f32(__ldcg(row + k_off + (size_t)h * D + d));
+        if (act) { qv = rnd<T>(silu_value(qv)); kv = rnd<T>(silu_value(kv)); }
+        qs[d] = qv;
+        ks[d] = kv;
+    }
+    float v4[4] = {0.f, 0.f, 0.f, 0.f};
+    if (col < V) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            v4[e] = to_f32(__ldcg(row + v_off + (size_t)h * V + col + e));
+            if (act) v4[e] = rnd<T>(silu_value(v4[e]));
+        }
+    }
+    __syncthreads();
+    float* S = state + ((size_t)__ldcg(seq_slots + b) * H + h) * D * V;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (col < V) {
+#pragma unroll 4
+        for (int d = w; d < D; d += LT_WARPS) {
+            float4 s4 = __ldcg(reinterpret_cast<const float4*>(S + (size_t)d * V + col));
+            const float kd = ks[d], qd = qs[d];
+            s4.x = fmaf(a, s4.x, kd * v4[0]); s4.y = fmaf(a, s4.y, kd * v4[1]);
+            s4.z = fmaf(a, s4.z, kd * v4[2]); s4.w = fmaf(a, s4.w, kd * v4[3]);
+            acc[0] = fmaf(s4.x, qd, acc[0]); acc[1] = fmaf(s4.y, qd, acc[1]);
+            acc[2] = fmaf(s4.z, qd, acc[2]); acc[3] = fmaf(s4.w, qd, acc[3]);
+            *reinterpret_cast<float4*>(S + (size_t)d * V + col) = s4;
+        }
+    }
+    *reinterpret_cast<float4*>(part + w * 128 + lane * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    __syncthreads();
+    for (int c = threadIdx.x; c < 128; c += LT_WARPS * 32) {
+        if (blockIdx.x * 128 + c >= V) continue;
+        float sum = 0.f;
+#pragma unroll
+        for (int p = 0; p < LT_WARPS; ++p) sum += part[p * 128 + c];
+        o[(size_t)b * H * V + (size_t)h * V + blockIdx.x * 128 + c] = sum;
+    }
+}
+
 // o [n, H * V] float; qkv [n, ld] of T with the heads' queries from column q_off on (H * D of them), keys from k_off, values
 // from v_off (H * V); state [slots, H, D, V] float; decay [H] float; cu_seqlens [B + 1], seq_slots [B] (n_tokens in all). act: 1 = SiLU.
 extern "C" int ti_lightning_scan(float* o, const void* qkv, long long ld, int q_off, int k_off, int v_off, float* state, const float* decay,
@@ -187,6 +244,12 @@ extern "C" int ti_lightning_scan(float* o, const void* qkv, long long ld, int q_
     if (B == 0) return 0;
     TI_REQUIRE(H > 0 && D > 0 && V > 0 && D <= LS_MAX_DIM, "lightning_scan: %d heads of %d x %d (the key size is at most %d)", H, D, V, LS_MAX_DIM);
     TI_REQUIRE(H <= 65535 && B <= 65535, "lightning_scan: %d heads, %d sequences", H, B);
+    if (n_tokens == B && V % 4 == 0 && D <= 2048) {      // one token per sequence: the kernel that streams the states
+        const size_t smem1 = (size_t)(2 * D + LT_WARPS * 128) * sizeof(float);
+        TI_DISPATCH_DTYPE(dtype, (ti_launch(lightning_token_kernel<T>, dim3((V + 127) / 128, H, B), dim3(LT_WARPS * 32), smem1, stream, o, (const T*)qkv, ld,
+                                            q_off, k_off, v_off, state, decay, seq_slots, H, D, V, act)));
+        return ti_check_launch("lightning_scan");
+    }
     // A launch with few blocks (one prompt of a model with few heads) shares the rows of S out between two blocks each.
     const int col_blocks = (V + LS_COLS - 1) / LS_COLS;
     const int split = ((long long)col_blocks * H * B < 100 && D >= 16) ? 2 : 1;
