@@ -266,7 +266,8 @@ def test_lightning_scan_alone(dtype):
     from tileinfer_b200.kernels import ops
     T = DTYPES[dtype]
     g = torch.Generator().manual_seed(5)
-    for H, D, V, lens in ((3, 12, 20, [1, 37, 5]), (2, 130, 33, [70]), (1, 256, 64, [3, 18]), (5, 8, 96, [16, 17, 15, 1])):
+    for H, D, V, lens in ((3, 12, 20, [1, 37, 5]), (2, 130, 33, [70]), (1, 256, 64, [3, 18]), (5, 8, 96, [16, 17, 15, 1]), (2, 400, 36, [1, 1]),
+                          (1, 512, 32, [40]), (3, 24, 132, [1, 1, 1, 1])):
         n = sum(lens)
         rows_ = plain.rnd(torch.randn(n, 2 * H * D + H * V + 7, generator=g).to(F64), T).to(T)
         decay = torch.rand(H, generator=g) * 0.5 + 0.5
@@ -403,6 +404,32 @@ def test_every_attention_kernel_counts_the_sink():
             err = (got - ref).abs().max(-1).values
             assert float(err.max()) <= 6 * 2.0 ** -8 * float(ref.abs().max()), \
                 f"{kernels} {lens} sequence {i}: worst at {int(err.argmax())}: {float(err.max()):.3g} (scale {float(ref.abs().max()):.3g}); first bad {int((err > 6 * 2.0 ** -8 * float(ref.abs().max())).float().argmax())}"
+
+
+@pytest.mark.parametrize("dtype", sorted(DTYPES))
+def test_models_of_one_kind_of_layer_and_of_one_layer(dtype):
+    """Layers of lightning alone (a cache without pages), of attention alone (no state but the taps'), a single layer without
+    feed-forward: whole, in portions and decoded, against the plain implementation."""
+    T = DTYPES[dtype]
+    cases = {
+        "lightning only": {"architecture": "Zudepel", "vocab": 61, "width": 48, "norm": {"eps": 1e-6},
+                           "layers": [zc.lightning(2, 8, 12, [0.9, 0.6], zc.dense(40)), zc.lightning(3, 16, 4, [0.99, 0.5, 0.8], None)]},
+        "attention only": {"architecture": "Zudepel", "vocab": 61, "width": 48, "norm": {"eps": 1e-6},
+                           "layers": [zc.attention(4, 2, 8, 12, 0.3, zc.dense(40), conv=2, rot=(4, 50.0)),
+                                      zc.attention(4, 2, 8, 12, 0.3, None, conv=3, rot=(4, 50.0), kv_from=0)]},
+        "one layer": {"architecture": "Zudepel", "vocab": 33, "width": 32, "norm": {"eps": 1e-6}, "layers": [zc.lightning(1, 32, 32, [0.95], None)]},
+    }
+    with tempfile.TemporaryDirectory() as tmp:
+        for name, case in cases.items():
+            zc.CASES[name] = case
+            try:
+                m = zc.Model(name, 3, tmp)
+            finally:
+                del zc.CASES[name]
+            engine = m.engine(dtype, max_tokens=512, max_seqs=2, max_context=256)
+            tokens = zc.prompts(m.vocab, [130], 5)[0]
+            for cuts in ([130], [2, 64, 3], [70, 1, 1, 58]):
+                zc.compare(m, tokens, run_cut(engine, tokens, cuts), T, f"{name} {dtype} {cuts}")
 
 
 # ---------------------------------------------------------------- through the public entry points

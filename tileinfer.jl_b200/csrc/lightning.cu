@@ -23,7 +23,7 @@
 
 #define LS_COLS 32
 #define LS_TOKENS 16
-#define LS_MAX_DIM 256
+#define LS_MAX_DIM 512
 
 __device__ __forceinline__ float silu_value(float z) { return z / (1.0f + expf(-z)); }
 
@@ -286,7 +286,8 @@ extern "C" int ti_lightning_scan(float* o, const void* qkv, long long ld, int q_
         if (dp <= 4) LS_LAUNCH(4);
         else if (dp <= 8) LS_LAUNCH(8);
         else if (dp <= 16) LS_LAUNCH(16);
-        else LS_LAUNCH(32);
+        else if (dp <= 32) LS_LAUNCH(32);
+        else LS_LAUNCH(64);
     });
 #undef LS_LAUNCH2
 #undef LS_LAUNCH
