@@ -146,3 +146,14 @@ def test_plain_pieces():
     chosen, w, _ = plain.route(h, W, "r.", mlp, torch.float32)
     s = torch.softmax(h, -1)[0]
     assert chosen.tolist() == [[2, 3]] and abs(float(w[0, 1]) - float(s[3] / (s[2] + s[3]))) < 1e-12
+
+
+def test_the_command_line_writes_a_model_folder_of_this_design(tmp_path, capsys):
+    """``tileinfer random config.json out`` goes through the registry: a Zudepel config.json gives a folder that loads back."""
+    from tileinfer_b200.cli import cli
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(zc.CASE_C))
+    out = tmp_path / "model"
+    assert cli(["random", str(cfg_path), str(out), "--seed", "3"]) == 0
+    cfg, W = zc.load_folder(str(out))
+    assert cfg["architecture"] == "Zudepel" and W["l1.mix.norm"].shape == (16,) and W["l1.mlp.router"].shape == (4, 64)
