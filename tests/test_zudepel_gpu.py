@@ -298,7 +298,7 @@ def test_router_with_groups_corrections_and_pass_through_choices_alone(dtype):
     from tileinfer_b200.kernels import ops
     T = DTYPES[dtype]
     g = torch.Generator().manual_seed(9)
-    for E, I, top, groups, keep, always in ((6, 2, 3, 4, 2, 2), (16, 4, 4, 4, 3, 1), (5, 0, 1, 1, 1, 0), (3, 1, 4, 1, 1, 0), (8, 4, 2, 6, 1, 1)):
+    for E, I, top, groups, keep, always in ((6, 2, 3, 4, 2, 2), (15, 5, 3, 5, 2, 1), (5, 0, 1, 1, 1, 0), (3, 1, 4, 1, 1, 0), (8, 4, 2, 6, 1, 1)):
         n, width, total = 70, 24, E + I
         h = plain.rnd(torch.randn(n, width, generator=g).to(F64), T)
         wr = plain.rnd(torch.randn(total + 1, width, generator=g).to(F64) * 0.7, T)

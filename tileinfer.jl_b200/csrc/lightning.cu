@@ -52,8 +52,8 @@ __global__ void __launch_bounds__(LS_COLS* LS_PARTS) lightning_scan_kernel(
         const int d = row0 + w * DP + i;
         s[i] = (d < row1 && col < V) ? __ldcg(S + (size_t)d * V + col) : 0.f;
     }
-    // The rows of a round come in 16-byte vectors where the layout allows it, and the next round's are asked for before
-    // this round's arithmetic, so that their way from memory is hidden behind it.
+    // The rows of a batch of 16 tokens come in 16-byte vectors where the layout allows it, and the next batch's are asked for
+    // before this batch's arithmetic, so that their way from memory is hidden behind it.
     constexpr int VEC = 16 / (int)sizeof(T), MAXV = 4;
     const bool wide = VECTORS && D % VEC == 0 && V % VEC == 0;
     const int qk_vecs = D / VEC;                        // vectors in a head's row of q (and of k)
@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(LS_COLS* LS_PARTS) lightning_scan_kernel(
     if (wide && t0 < t1) fetch(t0, min(LS_TOKENS, t1 - t0));
     for (int base = t0; base < t1; base += LS_TOKENS) {
         const int count = min(LS_TOKENS, t1 - base);
-        __syncthreads();                                // the last round's readers are done
+        __syncthreads();                                // the last batch's readers are done
         if (wide) {
 #pragma unroll
             for (int i = 0; i < MAXV; ++i) {
@@ -260,7 +260,7 @@ extern "C" int ti_lightning_scan(float* o, const void* qkv, long long ld, int q_
     const int parts = ((long long)col_blocks * split * H * B <= 160 && n_tokens >= 64 * B) ? 16 : 8;
     const size_t smem = (size_t)(2 * LS_TOKENS * D + LS_TOKENS * LS_COLS + LS_TOKENS * parts * LS_COLS) * sizeof(float);
     const int dp = ((D + split - 1) / split + parts - 1) / parts;
-    // 16-byte loads need every row's pieces on 16-byte borders and at most four vectors of q per thread and round.
+    // 16-byte loads need every row's pieces on 16-byte borders and at most four vectors of q per thread and batch of tokens.
 #define LS_LAUNCH2(DP, PARTS)                                                                                                        \
     do {                                                                                                                             \
         constexpr int VEC = 16 / (int)sizeof(T);                                                                                     \
