@@ -13,8 +13,8 @@
 //
 // The scan: the columns of S are independent (column j of S sees v_t[j] only), so a block owns 32 columns of one
 // (sequence, head) and walks the sequence's tokens in order; its 8 or 16 warps split the rows of S (warp w owns DP rows in a
-// row, read from shared memory four at a time), a lane owns one column, the state lives in registers. Tokens are staged 16 at a time in shared memory; the
-// warps' partial sums of o meet there once per 16 tokens. A launch of few blocks (one prompt, few heads) shares the rows of S
+// row, read from shared memory four at a time), a lane owns one column, the state lives in registers. Tokens are staged 32 at a time in shared memory; the
+// warps' partial sums of o meet there once per 32 tokens. A launch of few blocks (one prompt, few heads) shares the rows of S
 // out between two blocks per column block, whose two shares of o are added in global memory. A token's result depends on
 // the sequence's earlier tokens alone; the order of its sums depends on the sizes and on whether the launch was shared
 // out, so results agree to rounding, not bit for bit, between a prompt alone and the same prompt in a large batch.
@@ -22,7 +22,7 @@
 #include "common.cuh"
 
 #define LS_COLS 32
-#define LS_TOKENS 16
+#define LS_TOKENS 32
 #define LS_MAX_DIM 512
 
 __device__ __forceinline__ float silu_value(float z) { return z / (1.0f + expf(-z)); }
@@ -84,7 +84,8 @@ __global__ void __launch_bounds__(LS_COLS* LS_PARTS) lightning_scan_kernel(
     if (wide && t0 < t1) fetch(t0, min(LS_TOKENS, t1 - t0));
     for (int base = t0; base < t1; base += LS_TOKENS) {
         const int count = min(LS_TOKENS, t1 - base);
-        __syncthreads();                                // the last batch's readers are done
+        // (No barrier here: every thread has passed the barrier after the last batch's arithmetic, so its rows may be
+        // overwritten; the shares of o that slow threads may still be adding up are rewritten only after the next barrier.)
         if (wide) {
 #pragma unroll
             for (int i = 0; i < MAXV; ++i) {
